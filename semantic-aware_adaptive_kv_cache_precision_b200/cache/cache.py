@@ -184,7 +184,9 @@ class SequenceCache:
                                     "that this cache takes per sequence; nothing was taken")
                 first = int(self._front[g][s]) // BLOCK
                 last = -(-int(n) // BLOCK)
-                missing = [b for b in range(first, last) if group.tables[s, b] < 0]
+                kept = -(-int(group.need.keep_first or 0) // BLOCK)     # never given back
+                missing = [b for b in list(range(min(kept, first, last)))
+                           + list(range(first, last)) if group.tables[s, b] < 0]
                 want.append((s, missing))
             total = sum(len(m) for _, m in want)
             if total > group.pool.free:
@@ -210,6 +212,8 @@ class SequenceCache:
                 old = int(self._front[g][s]) // BLOCK
                 if keep_from > old:
                     row = group.tables[s]
+                    # (the blocks of the first `keep_first` positions stay where they are)
+                    old = max(old, -(-int(group.need.keep_first or 0) // BLOCK))
                     gone = [int(b) for b in row[old:keep_from] if b >= 0]
                     row[old:keep_from] = -1
                     self._release(group, gone)

@@ -18,12 +18,15 @@ class KVNeed:
     values at all; the entry is one tensor per position (a mixer that caches a single
     latent and makes keys and values from it). `dtype` None: the type of the activations;
     'float32', 'bfloat16' or 'int32' fixes it whatever the engine's mode. Entries with the
-    same need share a group, that is, a block pool and block lists."""
+    same need share a group, that is, a block pool and block lists. `keep_first` k (with a
+    window): the blocks that hold positions below k are never given back (a window that keeps
+    a sequence's first tokens)."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
     dtype: Optional[str] = None
+    keep_first: int = 0
 
     @property
     def value_width(self) -> int:

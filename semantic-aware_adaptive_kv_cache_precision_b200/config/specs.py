@@ -27,11 +27,13 @@ class ConfigError(ValueError):
 class NormSpec:
     """`kind` "rms_norm": x / sqrt(mean(x^2) + eps) * w; "layer_norm": (x - mean) /
     sqrt(variance + eps) * w, no bias. `suffix` is what the norm's weight is called after
-    the norm's own name (".weight" in most checkpoints, nothing in some)."""
+    the norm's own name (".weight" in most checkpoints, nothing in some). `offset` is added
+    to the stored weight before it multiplies: 1.0 for weights stored around zero."""
     size: int
     eps: float
     kind: str = "rms_norm"
     suffix: str = ".weight"
+    offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -49,15 +51,28 @@ class RampScaling:
 
 
 @dataclass(frozen=True)
+class BandScaling:
+    """Stretching of a rotation's long wavelengths by bands of wavelength (the scheme of
+    Llama 3.1): a frequency f whose wavelength l = 2 pi / f is shorter than `original / high`
+    stays, one longer than `original / low` becomes f / `factor`, and between the two it is
+    `(1 - s) f / factor + s f` with `s = (original / l - low) / (high - low)`. Cosines and
+    sines keep their size."""
+    factor: float
+    original: float
+    low: float
+    high: float
+
+
+@dataclass(frozen=True)
 class RotarySpec:
     """Rotate-half rotary position encoding of the first `rotary_dim` of each head;
-    `scaling` (a `RampScaling`) stretches its long wavelengths."""
+    `scaling` (a `RampScaling` or a `BandScaling`) stretches its long wavelengths."""
     head_dim: int
     rotary_dim: int
     theta: float
     max_positions: int
     kind: str = "rotary_half"
-    scaling: Optional[RampScaling] = None
+    scaling: Optional[object] = None
 
 
 @dataclass(frozen=True)
@@ -87,6 +102,8 @@ class GatedMLPSpec:
     activation: str
     bias: bool = False
     kind: str = "gated_mlp"
+    #: the three tensors' names after the part's prefix: gate, up, down
+    names: tuple = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
 
 
 @dataclass(frozen=True)
@@ -227,6 +244,99 @@ class RoutedExpertsSpec:
 
 
 @dataclass(frozen=True)
+class WindowSinkAttentionSpec:
+    """Grouped-query causal attention over a sliding window that also keeps a sequence's first
+    tokens, with a learned logit a head in the softmax's denominator:
+
+        query i sees key j <= i  if  i - j < window  or  j < keep_first
+        weights_ij = exp(s_ij) / (sum_visible exp(s_ij') + exp(sink[h])),   s_ij = q_i . k_j * scale
+
+    (`window` None: every earlier key; `sink` False: the plain softmax). Kept tokens keep their
+    true positions. `qk_norm` "whole": queries and keys are each divided by the root mean square
+    of their WHOLE projection (all heads together, `eps` inside the root) and multiplied by a
+    weight of that size, before the rotation; None: no norm. `position`: a rotation of the first
+    `rotary_dim` numbers of every head, or None. Values may have a width of their own; `bias`:
+    q, k, v have biases. The heads' outputs are multiplied by `out_scale` before the output
+    projection.
+
+    Tensor names after the part's prefix: `q`, `k`, `v` (+ `.b`), `q.norm`, `k.norm`, `sink`, `o`."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    window: Optional[int]
+    keep_first: int
+    eps: float
+    position: Optional[RotarySpec]
+    sink: bool = True
+    qk_norm: Optional[str] = "whole"
+    bias: bool = True
+    out_scale: float = 1.0
+    kind: str = "window_sink_attention"
+
+
+@dataclass(frozen=True)
+class DecayAttentionSpec:
+    """Attention without softmax whose state, one `head_dim x value_dim` matrix a head, fades by
+    a fixed factor a head:
+
+        S <- decay[h] S + k v^T,   o = S^T q,        q, k, v = silu of their projections
+
+    All heads' outputs together are divided by their root mean square (`eps` inside the root),
+    multiplied by a weight, by `sigmoid(Wg x)` element by element (`gate`) and by `out_scale`,
+    and projected.
+
+    Tensor names after the part's prefix: `q`, `k`, `v`, `g`, `norm`, `o`."""
+    hidden: int
+    heads: int
+    head_dim: int
+    value_dim: int
+    decay: tuple
+    eps: float
+    gate: bool = True
+    out_scale: float = 1.0
+    kind: str = "decay_attention"
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Two mixers side by side that read the same input; the mixer's output is the sum of
+    theirs (each already multiplied by its own `out_scale`). Both must offer the branch
+    interface (`input_decls`, `mix`, `w_o`): their input matrices are one product.
+
+    Tensor names: the branches' own, after the part's prefix + `names[i]` + "."."""
+    hidden: int
+    left: object
+    right: object
+    names: tuple = ("left", "right")
+    kind: str = "parallel_mixer"
+
+
+@dataclass(frozen=True)
+class SelectiveScanSpec:
+    """The selective-scan mixer (Mamba): `[x | z] = Win h`; x passes a causal convolution a
+    channel over `taps` tokens (last column: the current token; zeros before the start) and
+    silu; `[dt | B | C] = Wx x` with dt `dt_rank` wide; `dt = softplus(Wdt dt + b)`, one a
+    channel; `A = -exp(A_log)`; per channel c and state n
+
+        S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n;   y_c = sum_n S[c, n] C_n + D_c x_c
+
+    and the output is `Wo [y * silu(z)]`. State a sequence: S (fp32) and the convolution's last
+    `taps - 1` inputs.
+
+    Tensor names after the part's prefix: `in`, `conv`, `conv.b`, `x`, `dt`, `dt.b`, `A_log`,
+    `D`, `o`."""
+    hidden: int
+    inner: int
+    state: int
+    dt_rank: int
+    taps: int
+    kind: str = "selective_scan"
+
+
+@dataclass(frozen=True)
 class DenseMLPSpec:
     """Dense feed-forward without a gate: `down(act(up(x)))`; tensors `up` and `down`."""
     hidden: int
@@ -298,6 +408,24 @@ class SandwichBlockSpec:
     ffn_name: str = "mlp"
     norm_names: tuple = ("norm1", "norm1b", "norm2", "norm2b")
     kind: str = "sandwich_block"
+
+
+@dataclass(frozen=True)
+class OutputNormBlockSpec:
+    """A layer whose sublayers read the residual stream itself and whose norms sit on the
+    sublayers' OUTPUTS only:
+
+        x += norm1(mixer(x));   x += norm2(ffn(x))
+
+    `ffn` None: the layer has no feed-forward (and no `norm2`)."""
+    prefix: str
+    mixer: object
+    ffn: object
+    norm: NormSpec
+    mixer_name: str = "mix"
+    ffn_name: str = "mlp"
+    norm_names: tuple = ("norm1", "norm2")
+    kind: str = "output_norm_block"
 
 
 @dataclass(frozen=True)

@@ -55,6 +55,11 @@ struct AttentionExtra {
   // chunk of its keys through shared memory as a prompt's consecutive tokens do (the rows are
   // read once for all of the token's heads); `key_splits` blocks take ranges of the chunks.
   int heads_first;
+  // A window that keeps a sequence's first tokens: key j < keep is seen by every later query
+  // whatever the window says (it keeps its own position). With `sink` (fp32, one number a
+  // head) the softmax's denominator also holds exp(sink[h]): a logit without key or value.
+  int keep;
+  const float* sink;
 };
 
 namespace {
@@ -75,6 +80,18 @@ __device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
   if (chunk > 0) return pos - pos % chunk;
   return (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
 }
+
+// The chunks of 32 positions that hold visible keys, as a list: the chunks of the kept first
+// tokens that lie before the window's first chunk, then the window's chunks up to `last`.
+struct ChunkList {
+  int kept, from, count;
+  __device__ __forceinline__ ChunkList(int first, int last, int keep) {
+    from = first / 32;
+    kept = (keep + 31) / 32 < from ? (keep + 31) / 32 : from;
+    count = kept + last / 32 - from + 1;
+  }
+  __device__ __forceinline__ int at(int i) const { return i < kept ? i : from + i - kept; }
+};
 
 template <typename T>
 __global__ void kv_store_kernel(const T* __restrict__ qkv, long long stride, int k_off, int v_off,
@@ -302,7 +319,7 @@ distance_attention_tiled_kernel(
     // columns, rows `vstride` apart (in the cache, or in the block's copy of the chunk)
     auto chunk = [&](int c, const T* kp, const T* vp, int vstride) {
       const int j = c * 32 + lane;
-      const bool valid = j >= first && j <= pos;
+      const bool valid = (j >= first || j < x.keep) && j <= pos;
       float s[P];
 #pragma unroll
       for (int p = 0; p < P; ++p) s[p] = 0.f;
@@ -360,7 +377,7 @@ distance_attention_tiled_kernel(
 #pragma unroll
         for (int i = 0; i < VPL; ++i) acc[p][i] *= corr;
       }
-      const int lo = first - c * 32 > 0 ? first - c * 32 : 0;
+      const int lo = (first - c * 32 > 0 && c * 32 >= x.keep) ? first - c * 32 : 0;
       const int hi = pos - c * 32 < 31 ? pos - c * 32 : 31;
       for (int k0 = lo; k0 <= hi; k0 += 4) {         // four values' rows in flight at a time
         alignas(16) T got[4][VPL];
@@ -413,8 +430,10 @@ distance_attention_tiled_kernel(
     };
     if (!staged) {
       // (with split keys, whatever the form: block y takes every key_splits-th turn)
-      const int c0 = first / 32 + (x.key_splits > 1 ? (int)blockIdx.y * splits : 0) + split;
-      for (int c = c0; c <= pos / 32; c += splits * (x.key_splits > 1 ? x.key_splits : 1)) {
+      const ChunkList list(first, pos, x.keep);
+      const int i0 = (x.key_splits > 1 ? (int)blockIdx.y * splits : 0) + split;
+      for (int ci = i0; ci < list.count; ci += splits * (x.key_splits > 1 ? x.key_splits : 1)) {
+        const int c = list.at(ci);
         const long long rows = rows_of(c);
         if (stage_ok == 2) {
           // a decoded token: the warp copies its chunk's rows into shared memory with every
@@ -453,7 +472,8 @@ distance_attention_tiled_kernel(
       const int kstride = k_row + kPiece;            // padded: the lanes' rows hit different banks
       T* stage = reinterpret_cast<T*>(shared + (long long)warps * P * row_floats);
       const int per_buffer = 32 * (kstride + (x.v_in_k ? 0 : vdim));
-      int c_lo = block_first / 32, c_hi = block_last / 32;
+      const ChunkList list(block_first, block_last, x.keep);
+      int c_lo = 0, c_hi = list.count - 1;           // (places in the block's list of chunks)
       if (key_parts > 1) {               // a contiguous share of the chunks for this block
         const int share = (c_hi - c_lo + key_parts) / key_parts;
         c_lo += key_part * share;
@@ -474,14 +494,15 @@ distance_attention_tiled_kernel(
         }
         copies_commit();
       };
-      if (c_lo <= c_hi) fetch(c_lo, 0);
+      if (c_lo <= c_hi) fetch(list.at(c_lo), 0);
       int buffer = 0;
-      for (int c = c_lo; c <= c_hi; ++c, buffer ^= 1) {
-        if (c < c_hi) fetch(c + 1, buffer ^ 1);
+      for (int ci = c_lo; ci <= c_hi; ++ci, buffer ^= 1) {
+        const int c = list.at(ci);
+        if (ci < c_hi) fetch(list.at(ci + 1), buffer ^ 1);
         else copies_commit();
         copies_wait_all_but_last();
         __syncthreads();
-        if (c >= first / 32 && c <= pos / 32) {
+        if ((c >= first / 32 || c * 32 < x.keep) && c <= pos / 32) {
           const T* ks = stage + buffer * per_buffer;
           if (x.v_in_k) chunk(c, ks + lane * kstride, ks + lane * VPL, kstride);
           else chunk(c, ks + lane * kstride, ks + 32 * kstride + lane * VPL, vdim);
@@ -569,9 +590,22 @@ distance_attention_tiled_kernel(
         for (int i = 0; i < VPL; ++i)
           if (lane * VPL + i < vdim) sum[i] = fmaf(__ldcg(row + 2 + lane * VPL + i), f, sum[i]);
       }
+      m[p] = top;
       l[p] = total;
 #pragma unroll
       for (int i = 0; i < VPL; ++i) acc[p][i] = sum[i];
+    }
+  }
+  if (x.sink != nullptr) {             // one more logit in the denominator, counted once
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      if (p >= np) continue;
+      const float s = x.sink[(h0 + p) / MAPS];
+      const float m_new = fmaxf(m[p], s);
+      const float corr = expf(m[p] - m_new);
+      l[p] = fmaf(l[p], corr, expf(s - m_new));
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) acc[p][i] *= corr;
     }
   }
   if constexpr (MAPS == 2) {
@@ -612,7 +646,7 @@ distance_attention_tiled_kernel(
       const float z = widen(qkv[(long long)t * stride + gate_off + h0 + p]);
       gate = 1.f / (1.f + expf(-z));
     }
-    const float inv = gate / l[p];
+    const float inv = gate * x.out_scale / l[p];
 #pragma unroll
     for (int i = 0; i < VPL; ++i)
       if (lane * VPL + i < vdim)
@@ -834,7 +868,8 @@ SAKV_EXPORT int sakv_cached_attention(
     int max_blocks, int tokens, int heads, int kv_heads, int maps, int dim, int vdim, float scale,
     int window, int chunk, float lambda, float out_scale, float eps, int gate_elem_off,
     int splits, int key_splits, float* scratch, long long scratch_floats, int* tickets,
-    int warp_stage, int heads_first, cudaStream_t stream) {
+    int warp_stage, int heads_first, int keep_first, const float* sink, cudaStream_t stream) {
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return cudaErrorInvalidValue;
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
       dim > 640 || vdim > 512 || max_blocks <= 0 || window < 0 || chunk < 0 ||
       (window > 0 && chunk > 0) || splits < 1 || splits > 16 || (maps != 1 && maps != 2) ||
@@ -864,6 +899,8 @@ SAKV_EXPORT int sakv_cached_attention(
   x.tickets = tickets;
   x.warp_stage = warp_stage;
   x.heads_first = heads_first && splits == 1;
+  x.keep = window > 0 ? keep_first : 0;
+  x.sink = sink;
   const void* values = x.v_in_k ? k_cache : v_cache;
   if (dtype == SAKV_F32)
     return pick_tiled<float>(qkv, stride, gate_off, out, k_cache, values, positions, token_seq,

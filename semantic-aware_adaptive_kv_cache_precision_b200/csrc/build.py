@@ -53,6 +53,9 @@ LIBRARIES = {
     "layer_norm": "layer_norm.cu",
     "latent": "latent.cu",
     "moe": "moe.cu",
+    "norm_update": "norm_update.cu",
+    "qk_prepare": "qk_prepare.cu",
+    "recurrent_scan": "recurrent_scan.cu",
 }
 
 #: extra flags of single libraries (libraries that need the driver API, for instance)

@@ -16,6 +16,7 @@ from .linear import Deferred, gated_up, linear, per_head
 from . import gemm_tc
 from .streams import streams_spread, streams_step, token_shift
 from .recurrent import delta_rule
+from .scan import causal_conv, decay_attention, norm_gate, selective_scan, step_size
 from . import mixture
 from .mixture import latent_prepare, rotate_heads
 from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
@@ -29,7 +30,8 @@ __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "att
            "decode_splits", "plan_token_blocks", "fast_path_takes", "forget_descriptors",
            "kernel_errors", "gated_silu", "gelu_tanh", "streams_step", "streams_spread", "token_shift",
            "delta_rule", "kv_store", "layer_norm", "cached_attention", "mixture", "latent_prepare",
-           "rotate_heads", "distance_attention", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "per_head", "choose", "Deferred"]
+           "rotate_heads", "distance_attention", "rms_update", "qk_prepare", "causal_conv",
+           "decay_attention", "norm_gate", "selective_scan", "step_size", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "per_head", "choose", "Deferred"]
 
 
 def _check(cond: bool, message: str) -> None:
@@ -246,6 +248,88 @@ def layer_norm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out_dty
     return out
 
 
+def rms_update(x: torch.Tensor, y: torch.Tensor | None = None,
+               add_weight: torch.Tensor | None = None, add_offset: float = 0.0,
+               out_dtype: torch.dtype | None = None, out_weight: torch.Tensor | None = None,
+               out_offset: float = 0.0, eps: float = 0.0,
+               rows: torch.Tensor | None = None) -> torch.Tensor | None:
+    """On rows of the fp32 stream `x`, in one pass: with `y` (fp32, x's shape), `x += y /
+    rms(y) * (add_offset + add_weight)`; with `out_dtype`, returns the rows of x in that type,
+    or with `out_weight` their RMS norm `x / rms(x) * (out_offset + out_weight)`; `rows`
+    (int32; only without `y`): those rows only. rms(v) = sqrt(mean(v^2) + eps)."""
+    require_cuda(x, y, add_weight, out_weight, rows)
+    _check(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x: fp32 [T, hidden]")
+    hidden = x.shape[1]
+    for w in (add_weight, out_weight):
+        _check(w is None or (w.shape == (hidden,) and w.is_contiguous()), "weight: [hidden]")
+    _check(y is not None or out_dtype is not None, "rms_update: nothing to do")
+    if y is not None:
+        _check(rows is None and add_weight is not None and y.dtype == torch.float32
+               and y.is_contiguous() and y.shape == x.shape, "y: fp32 like x, with a weight, no rows")
+    _check(add_weight is None or out_weight is None or add_weight.dtype == out_weight.dtype,
+           "the weights' types differ")
+    n = x.shape[0]
+    if rows is not None:
+        _check(rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous(),
+               "rows: int32 [R]")
+        n = rows.numel()
+    out = None if out_dtype is None else torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+    some = add_weight if add_weight is not None else out_weight
+    call("sakv_rms_update", ptr(x), ptr(y), ptr(add_weight), float(add_offset), ptr(rows),
+         ptr(out_weight), float(out_offset),
+         dtype_code(some.dtype) if some is not None else F32, ptr(out),
+         dtype_code(out_dtype if out_dtype is not None else torch.float32), n, hidden, float(eps))
+    return out
+
+
+def qk_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int,
+               dim: int, vdim: int, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None,
+               eps: float, cos: torch.Tensor | None, sin: torch.Tensor | None,
+               positions: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
+               k_cache: torch.Tensor, v_cache: torch.Tensor, out_dtype: torch.dtype,
+               write_cache: bool = True) -> torch.Tensor:
+    """From a fused projection's fp32 output `proj` [T, columns] (queries at `q_off`, keys at
+    `k_off`, values at `v_off`): queries and keys each divided by the root mean square of their
+    whole projection and multiplied by `q_weight` / `k_weight` (None: no norm), the first
+    `2 * cos.shape[1]` numbers of every head turned by the token's position (None: no
+    rotation), keys and values stored in the cache blocks. Returns the queries [T, heads *
+    dim] of `out_dtype`."""
+    require_cuda(proj, q_weight, k_weight, cos, sin, positions, token_seq, block_table, k_cache,
+                 v_cache)
+    tokens = proj.shape[0]
+    _check(proj.dtype == torch.float32 and proj.dim() == 2 and proj.stride(1) == 1,
+           "proj: fp32 [T, columns] with contiguous rows")
+    _check(max(q_off + heads * dim, k_off + kv_heads * dim, v_off + kv_heads * vdim)
+           <= proj.shape[1], "queries, keys or values reach beyond proj's columns")
+    _check((q_weight is None) == (k_weight is None), "q_weight and k_weight come together")
+    if q_weight is not None:
+        _check(q_weight.shape == (heads * dim,) and k_weight.shape == (kv_heads * dim,)
+               and q_weight.is_contiguous() and k_weight.is_contiguous()
+               and q_weight.dtype == k_weight.dtype, "norm weights: [heads * dim], [kv_heads * dim]")
+    rot = 0
+    if cos is not None:
+        _check(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.dim() == 2
+               and cos.is_contiguous() and sin.is_contiguous() and cos.shape == sin.shape,
+               "cos, sin: fp32 [positions, rot / 2]")
+        rot = 2 * cos.shape[1]
+    for t, name in ((positions, "positions"), (token_seq, "token_seq")):
+        _check(t.dtype == torch.int32 and t.is_contiguous() and t.numel() == tokens,
+               f"{name}: int32 [T]")
+    _check(block_table.dtype == torch.int32 and block_table.dim() == 2
+           and block_table.is_contiguous(), "block_table: int32 [B, max_blocks]")
+    for c, width in ((k_cache, dim), (v_cache, vdim)):
+        _check(c.dtype == out_dtype and c.is_contiguous() and c.dim() == 4
+               and tuple(c.shape[1:]) == (kv_heads, CACHE_BLOCK, width),
+               "cache entry: [blocks, kv_heads, 64, width] of the queries' type")
+    q = torch.empty((tokens, heads * dim), dtype=out_dtype, device=proj.device)
+    call("sakv_qk_prepare", ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off),
+         ptr(q_weight), ptr(k_weight), dtype_code(q_weight.dtype) if q_weight is not None else F32,
+         float(eps), ptr(cos), ptr(sin), rot, ptr(positions), ptr(token_seq), ptr(block_table),
+         block_table.shape[1], ptr(q), ptr(k_cache), ptr(v_cache), dtype_code(out_dtype), tokens,
+         heads, kv_heads, dim, vdim, int(write_cache))
+    return q
+
+
 def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor | None,
                      positions: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
                      heads: int, dim: int, vdim: int, scale: float, *, maps: int = 1,
@@ -253,7 +337,8 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      window: int | None = None, chunk: int | None = None, lam: float = 0.0,
                      out_scale: float = 1.0, eps: float = 0.0, gate_elem_off: int | None = None,
                      splits: int = 1, key_splits: int = 1, warp_stage: bool = False,
-                     heads_first: bool = False) -> torch.Tensor:
+                     heads_first: bool = False, keep_first: int = 0,
+                     sink: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of every token of the step over its sequence's cache, in the general
     form of `csrc/attention_distance.cu`: scores, softmax weights and weighted sums in fp32.
 
@@ -263,7 +348,10 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     columns from `q_split` on come from q2. `k_cache`: [blocks, kv_heads, 64, k_row] with map
     m's key at column m * dim; `v_cache`: [blocks, kv_heads, 64, v_row] of which the first
     `vdim` are read, or None: the values are the first `vdim` columns of the key rows. `window`
-    (the last w keys) or `chunk` (keys of the query's own run of c positions) or neither. Two
+    (the last w keys) or `chunk` (keys of the query's own run of c positions) or neither;
+    with a window, `keep_first` k: the keys at positions below k stay visible to every later
+    query. `sink` (fp32 [heads]): the softmax's denominator of head h also holds
+    `exp(sink[h])`. With one map the output is multiplied by `out_scale`. Two
     maps are combined as `a1 - lam * a2`, divided by their root mean square over vdim (+ eps),
     times `out_scale`, times the sigmoid of the `vdim` numbers that lie `gate_elem_off + h *
     vdim` elements after the token's first query. Returns [T, heads * vdim] of q's type.
@@ -275,8 +363,11 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     are ONE token's groups of heads and share every chunk of its keys through shared memory, so
     the rows are read once for all the token's heads; `key_splits` blocks a token then take
     contiguous shares of the chunks."""
-    require_cuda(q, k_cache, v_cache, positions, token_seq, block_table, q2)
+    require_cuda(q, k_cache, v_cache, positions, token_seq, block_table, q2, sink)
     tokens = q.shape[0]
+    _check(sink is None or (sink.dtype == torch.float32 and sink.shape == (heads,)
+                            and sink.is_contiguous()), "sink: fp32 [heads]")
+    _check(keep_first >= 0 and not (keep_first and chunk), "keep_first goes with a window")
     _check(q.dim() == 3 and q.stride(2) == 1 and q.shape[1] == heads * maps
            and q.shape[2] >= (q_split if q2 is not None else dim),
            "q: [T, heads * maps, >= dim] with contiguous rows")
@@ -319,7 +410,7 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
          float(scale), int(window) if window else 0, int(chunk) if chunk else 0, float(lam),
          float(out_scale), float(eps), -1 if gate_elem_off is None else int(gate_elem_off),
          int(splits), int(key_splits), ptr(scratch), floats, ptr(tickets), int(warp_stage),
-         int(heads_first))
+         int(heads_first), int(keep_first) if window else 0, ptr(sink))
     return out
 
 

@@ -37,7 +37,18 @@ SIGNATURES = {
                                 [P, I, L, I, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P]),
     "sakv_cached_attention": ("attention_distance",
                               [P, I, L, I, P, L, I, I, I, P, P, I, P, I, P, P, P, I, I, I, I, I, I,
-                               I, F, I, I, F, F, F, I, I, I, P, L, P, I, I, P]),
+                               I, F, I, I, F, F, F, I, I, I, P, L, P, I, I, I, P, P]),
+    "sakv_rms_update": ("norm_update", [P, P, P, F, P, P, F, I, P, I, I, I, F, P]),
+    "sakv_qk_prepare": ("qk_prepare", [P, L, I, I, I, P, P, I, F, P, P, I, P, P, P, I, P, P, P,
+                                       I, I, I, I, I, I, I, P]),
+    "sakv_causal_conv": ("recurrent_scan", [P, L, P, P, I, P, P, P, P, P, I, I, I, I, P]),
+    "sakv_conv_state": ("recurrent_scan", [P, L, P, P, P, I, I, I, P]),
+    "sakv_step_size": ("recurrent_scan", [P, L, I, P, P, I, P, I, I, P]),
+    "sakv_selective_scan": ("recurrent_scan", [P, I, P, P, L, I, I, P, L, P, P, I, P, P, P, P,
+                                               I, I, I, I, I, P]),
+    "sakv_decay_attention": ("recurrent_scan", [P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, I,
+                                                P]),
+    "sakv_norm_gate": ("recurrent_scan", [P, P, I, P, L, P, I, I, I, F, F, P]),
     "sakv_layer_norm": ("layer_norm", [P, P, P, P, P, I, P, I, I, I, F, P]),
     "sakv_latent_prepare": ("latent", [P, L, I, I, I, P, P, I, F, P, P, P, I, P, P, P, P, I, I, I,
                                        P]),

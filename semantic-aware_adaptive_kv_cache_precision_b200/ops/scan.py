@@ -1,0 +1,128 @@
+"""The recurrences without feedback from the state into its own update, over a step's tokens
+(`csrc/recurrent_scan.cu`): the selective scan with its convolution and step sizes, and
+attention without softmax over a fading state with its norm and gate."""
+
+from __future__ import annotations
+
+import torch
+
+from ._lib import KernelError, call, dtype_code, ptr, require_cuda
+
+
+def _check(cond: bool, message: str) -> None:
+    if not cond:
+        raise KernelError(message)
+
+
+def causal_conv(xz: torch.Tensor, channels: int, weight: torch.Tensor,
+                bias: torch.Tensor | None, state: torch.Tensor, step, out_dtype: torch.dtype,
+                keep_state: bool = True) -> torch.Tensor:
+    """silu of the causal convolution a channel over the first `channels` columns of fp32 `xz`
+    [T, columns]: `weight` [channels, taps], whose last column multiplies the token itself.
+    `state`: fp32 [slots, taps - 1, channels], each sequence's last inputs, read and (with
+    `keep_state`) replaced. Returns [T, channels] of `out_dtype`."""
+    require_cuda(xz, weight, bias, state)
+    tokens, taps = xz.shape[0], weight.shape[1]
+    _check(xz.dtype == torch.float32 and xz.dim() == 2 and xz.stride(1) == 1
+           and xz.shape[1] >= channels, "xz: fp32 [T, >= channels] with contiguous rows")
+    _check(weight.shape == (channels, taps) and weight.is_contiguous(), "weight: [channels, taps]")
+    _check(bias is None or (bias.shape == (channels,) and bias.is_contiguous()
+                            and bias.dtype == weight.dtype), "bias: [channels] of the weight's type")
+    _check(state.dtype == torch.float32 and state.is_contiguous()
+           and tuple(state.shape[1:]) == (taps - 1, channels),
+           "state: fp32 [slots, taps - 1, channels]")
+    out = torch.empty((tokens, channels), dtype=out_dtype, device=xz.device)
+    call("sakv_causal_conv", ptr(xz), xz.stride(0), ptr(weight), ptr(bias),
+         dtype_code(weight.dtype), ptr(state), ptr(step.cu_seqlens), ptr(step.token_seq),
+         ptr(step.slots), ptr(out), dtype_code(out_dtype), tokens, channels, taps)
+    if keep_state and taps > 1:
+        call("sakv_conv_state", ptr(xz), xz.stride(0), ptr(state), ptr(step.cu_seqlens),
+             ptr(step.slots), step.sequences, channels, taps)
+    return out
+
+
+def step_size(low: torch.Tensor, rank: int, weight: torch.Tensor,
+              bias: torch.Tensor | None) -> torch.Tensor:
+    """fp32 [T, channels] = softplus(low[:, :rank] weight^T + bias), all in fp32."""
+    require_cuda(low, weight, bias)
+    channels = weight.shape[0]
+    _check(low.dtype == torch.float32 and low.dim() == 2 and low.stride(1) == 1
+           and low.shape[1] >= rank, "low: fp32 [T, >= rank] with contiguous rows")
+    _check(weight.shape == (channels, rank) and weight.is_contiguous(), "weight: [channels, rank]")
+    _check(bias is None or (bias.shape == (channels,) and bias.is_contiguous()
+                            and bias.dtype == weight.dtype), "bias: [channels] of the weight's type")
+    dt = torch.empty((low.shape[0], channels), dtype=torch.float32, device=low.device)
+    call("sakv_step_size", ptr(low), low.stride(0), int(rank), ptr(weight), ptr(bias),
+         dtype_code(weight.dtype), ptr(dt), low.shape[0], channels)
+    return dt
+
+
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, low: torch.Tensor, b_off: int, c_off: int,
+                   n_state: int, z: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+                   state: torch.Tensor, step, keep_state: bool = True) -> torch.Tensor:
+    """`S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n; y_c = sum_n S[c, n] C_n + D_c x_c`
+    over each sequence's tokens, A = -exp(a_log); returns `y * silu(z)` [T, channels] of x's
+    type. `x`: [T, channels]; `dt`: fp32 [T, channels]; B and C: `n_state` columns of fp32
+    `low` from `b_off` and `c_off`; `z`: fp32 [T, channels] (a view with any row stride);
+    `state`: fp32 [slots, channels, n_state], read and (with `keep_state`) left."""
+    require_cuda(x, dt, low, z, a_log, d_skip, state)
+    tokens, channels = x.shape
+    _check(x.is_contiguous() and dt.dtype == torch.float32 and dt.is_contiguous()
+           and dt.shape == x.shape, "x: [T, channels]; dt: fp32 of the same shape")
+    _check(low.dtype == torch.float32 and low.dim() == 2 and low.stride(1) == 1
+           and max(b_off, c_off) + n_state <= low.shape[1] and low.shape[0] == tokens,
+           "low: fp32 [T, columns] holding B and C")
+    _check(z.dtype == torch.float32 and z.shape == x.shape and z.stride(1) == 1,
+           "z: fp32 [T, channels] with contiguous rows")
+    _check(a_log.shape == (channels, n_state) and a_log.is_contiguous()
+           and d_skip.shape == (channels,) and d_skip.is_contiguous()
+           and d_skip.dtype == a_log.dtype, "a_log: [channels, n_state]; d_skip: [channels]")
+    _check(state.dtype == torch.float32 and state.is_contiguous()
+           and tuple(state.shape[1:]) == (channels, n_state), "state: fp32 [slots, channels, n_state]")
+    out = torch.empty_like(x)
+    call("sakv_selective_scan", ptr(x), dtype_code(x.dtype), ptr(dt), ptr(low), low.stride(0),
+         int(b_off), int(c_off), ptr(z), z.stride(0), ptr(a_log), ptr(d_skip),
+         dtype_code(a_log.dtype), ptr(state), ptr(step.cu_seqlens), ptr(step.slots), ptr(out),
+         tokens, step.sequences, channels, n_state, int(keep_state))
+    return out
+
+
+def decay_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, dim: int,
+                    vdim: int, decay_less_one: torch.Tensor, state: torch.Tensor, step,
+                    keep_state: bool = True) -> torch.Tensor:
+    """`S <- decay[h] S + k v^T; o = S^T q` a head over each sequence's tokens, with q, k, v =
+    silu of the columns of fp32 `proj` from `q_off`, `k_off` (heads * dim each) and `v_off`
+    (heads * vdim). `decay_less_one`: fp32 [heads] holding `decay - 1` (the kernel adds `(decay - 1) S + k
+    v^T` to S). `state`: fp32 [slots, heads, vdim, dim] (the state's transpose), read and (with
+    `keep_state`) left. Returns fp32 [T, heads * vdim]."""
+    require_cuda(proj, decay_less_one, state)
+    tokens = proj.shape[0]
+    _check(proj.dtype == torch.float32 and proj.dim() == 2 and proj.stride(1) == 1
+           and max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim) <= proj.shape[1],
+           "proj: fp32 [T, columns] holding q, k and v")
+    _check(decay_less_one.dtype == torch.float32 and decay_less_one.shape == (heads,)
+           and decay_less_one.is_contiguous(), "decay_less_one: fp32 [heads]")
+    _check(state.dtype == torch.float32 and state.is_contiguous()
+           and tuple(state.shape[1:]) == (heads, vdim, dim), "state: fp32 [slots, heads, vdim, dim]")
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
+    call("sakv_decay_attention", ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off),
+         ptr(decay_less_one), ptr(state), ptr(step.cu_seqlens), ptr(step.slots), ptr(out), tokens,
+         step.sequences, heads, dim, vdim, int(keep_state))
+    return out
+
+
+def norm_gate(y: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | None, eps: float,
+              scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """`y / sqrt(mean(y^2) + eps) * weight * sigmoid(gate) * scale` over whole rows of fp32 `y`
+    [T, width]; `gate`: fp32 [T, width] (a view with any row stride) or None."""
+    require_cuda(y, weight, gate)
+    tokens, width = y.shape
+    _check(y.dtype == torch.float32 and y.is_contiguous(), "y: contiguous fp32 [T, width]")
+    _check(weight.shape == (width,) and weight.is_contiguous(), "weight: [width]")
+    _check(gate is None or (gate.dtype == torch.float32 and gate.shape == y.shape
+                            and gate.stride(1) == 1), "gate: fp32 [T, width] with contiguous rows")
+    out = torch.empty((tokens, width), dtype=out_dtype, device=y.device)
+    call("sakv_norm_gate", ptr(y), ptr(weight), dtype_code(weight.dtype), ptr(gate),
+         0 if gate is None else gate.stride(0), ptr(out), dtype_code(out_dtype), tokens, width,
+         float(eps), float(scale))
+    return out

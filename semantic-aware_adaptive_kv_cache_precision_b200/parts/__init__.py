@@ -14,8 +14,15 @@ from .latent_attention import LatentAttention
 from .differential_attention import DifferentialAttention
 from .routed_experts import RoutedExperts
 from .sandwich import NormedUpdate, SandwichBlock
+from .window_sink_attention import WindowSinkAttention
+from .decay_attention import DecayAttention
+from .parallel_mixer import ParallelMixer
+from .selective_scan import SelectiveScanMixer
+from .output_norm import OutputNormBlock
 
 __all__ = ["Part", "build_part", "register_part", "RMSNorm", "RotaryHalf", "NoPosition",
            "GQAAttention", "GatedMLP", "DenseMLP", "PreNormBlock", "DeltaRuleMixer",
            "LogDistanceAttention", "StreamBlock", "StreamUpdate", "LayerNorm", "LatentAttention",
-           "DifferentialAttention", "RoutedExperts", "SandwichBlock", "NormedUpdate"]
+           "DifferentialAttention", "RoutedExperts", "SandwichBlock", "NormedUpdate",
+           "WindowSinkAttention", "DecayAttention", "ParallelMixer", "SelectiveScanMixer",
+           "OutputNormBlock"]

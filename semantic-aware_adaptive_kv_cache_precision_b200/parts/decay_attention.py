@@ -1,0 +1,107 @@
+"""Attention without softmax over a state that fades by a fixed factor a head
+(`DecayAttentionSpec`):
+
+    [q | k | v | g] = h Wfused^T;   q, k, v <- silu(q), silu(k), silu(v)
+    S <- decay[h] S + k v^T;   o = S^T q                        (a head; S is dim x value_dim)
+    out = Wo [ o / rms(o) * w * sigmoid(g) * out_scale ]        (rms over ALL heads' outputs)
+
+The fused projection leaves fp32 (its accumulator, unrounded); the silus, the recurrence, the
+norm and the gate are fp32 in both modes (`csrc/recurrent_scan.cu`). The state lives in the
+cache as fixed-size per-sequence state, stored as its transpose [heads, value_dim, dim].
+
+The part is a mixer of its own (`produce`) and a branch of a `ParallelMixer`.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.needs import StateNeed
+from ..weights.decl import TensorDecl
+from .base import Part, register_part
+
+
+class DecayAttention(Part):
+    kernel_libraries = ("recurrent_scan", "gemm_f32", "gemm_tc")
+
+    def __init__(self, spec, prefix, mode):
+        super().__init__(spec, prefix, mode)
+        s = spec
+        if s.head_dim > 256:
+            raise ValueError(f"head_dim {s.head_dim}: the recurrence kernel takes up to 256")
+        if len(s.decay) != s.heads:
+            raise ValueError(f"{len(s.decay)} decays for {s.heads} heads")
+        self.qk_cols = s.heads * s.head_dim
+        self.v_cols = s.heads * s.value_dim
+        self.decay_less_one = None
+
+    # -- what a branch offers -------------------------------------------------------------
+
+    def _inputs(self):
+        rows = [("q", self.qk_cols), ("k", self.qk_cols), ("v", self.v_cols)]
+        if self.spec.gate:
+            rows.append(("g", self.v_cols))
+        return tuple(rows)
+
+    @property
+    def input_rows(self) -> int:
+        return sum(rows for _, rows in self._inputs())
+
+    def input_decls(self, group):
+        s, p = self.spec, self.prefix
+        return [TensorDecl(p + n, (rows, s.hidden), group=group) for n, rows in self._inputs()]
+
+    def other_decls(self):
+        s, p = self.spec, self.prefix
+        return [TensorDecl(p + "norm", (self.v_cols,), init="ones_normal"),
+                TensorDecl(p + "o", (s.hidden, self.v_cols))]
+
+    def input_bias(self, arena):
+        return None
+
+    def bind_rest(self, arena):
+        p = self.prefix
+        self.norm_w, self.w_o = arena.view(p + "norm"), arena.view(p + "o")
+        # the kernel takes `decay - 1`, rounded to fp32 once from the exact number
+        self.decay_less_one = (torch.tensor(self.spec.decay, dtype=torch.float64) - 1.0).to(
+            device=self.w_o.device, dtype=torch.float32)
+
+    def mix(self, proj, offset, h, step, view, write_cache=True):
+        """From the fused product `proj` (fp32 [T, columns], this branch's columns from
+        `offset` on) to the input of `w_o`: [T, heads * value_dim] of the activations' type,
+        `out_scale` included."""
+        s = self.spec
+        k_off, v_off = offset + self.qk_cols, offset + 2 * self.qk_cols
+        y = ops.decay_attention(proj, offset, k_off, v_off, s.heads, s.head_dim, s.value_dim,
+                                self.decay_less_one, view.state, step, keep_state=write_cache)
+        gate = proj[:, v_off + self.v_cols:v_off + 2 * self.v_cols] if s.gate else None
+        return ops.norm_gate(y, self.norm_w, gate, s.eps, s.out_scale, self.act_dtype)
+
+    # -- the part alone ---------------------------------------------------------------------
+
+    def tensor_decls(self):
+        return self.input_decls(self.prefix + "fused") + self.other_decls()
+
+    def bind(self, arena):
+        p = self.prefix
+        self.w_in = arena.group_view(p + "fused")
+        if self.w_in is None:
+            self.w_in = torch.cat([arena.view(p + n) for n, _ in self._inputs()])
+        self.bind_rest(arena)
+
+    def cache_need(self):
+        s = self.spec
+        return StateNeed((s.heads, s.value_dim, s.head_dim), "float32")
+
+    def produce(self, h, step, view, write_cache=True):
+        """The mixer's output, fp32 [T, hidden]."""
+        proj = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        return ops.linear(self.mix(proj, 0, h, step, view, write_cache), self.w_o,
+                          out_dtype=torch.float32)
+
+    def forward(self, h, step, view, residual, write_cache=True):
+        ops.add_into(residual, self.produce(h, step, view, write_cache))
+
+
+register_part("decay_attention", DecayAttention)

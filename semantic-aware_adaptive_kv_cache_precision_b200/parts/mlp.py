@@ -22,17 +22,26 @@ class GatedMLP(Part):
 
     def tensor_decls(self):
         s, p = self.spec, self.prefix
-        return [TensorDecl(f"{p}gate_proj.weight", (s.intermediate, s.hidden), group=p + "gate_up"),
-                TensorDecl(f"{p}up_proj.weight", (s.intermediate, s.hidden), group=p + "gate_up"),
-                TensorDecl(f"{p}down_proj.weight", (s.hidden, s.intermediate))]
+        gate, up, down = self._names()
+        return [TensorDecl(p + gate, (s.intermediate, s.hidden), group=p + "gate_up"),
+                TensorDecl(p + up, (s.intermediate, s.hidden), group=p + "gate_up"),
+                TensorDecl(p + down, (s.hidden, s.intermediate))]
+
+    def _names(self):
+        return getattr(self.spec, "names",
+                       ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
 
     def bind(self, arena):
         p = self.prefix
+        gate, up, down = self._names()
         self.w_gate_up = arena.group_view(p + "gate_up")
         if self.w_gate_up is None:
-            self.w_gate_up = torch.cat([arena.view(p + "gate_proj.weight"),
-                                        arena.view(p + "up_proj.weight")])
-        self.w_down = arena.view(p + "down_proj.weight")
+            self.w_gate_up = torch.cat([arena.view(p + gate), arena.view(p + up)])
+        self.w_down = arena.view(p + down)
+
+    def produce(self, h, step):
+        """The feed-forward's output as a tensor of its own, fp32 [T, hidden]."""
+        return ops.linear(ops.gated_up(h, self.w_gate_up), self.w_down, out_dtype=torch.float32)
 
     can_defer = True
 

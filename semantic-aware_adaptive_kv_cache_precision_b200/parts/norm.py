@@ -1,5 +1,7 @@
 """RMSNorm: `x * rsqrt(mean(x^2) + eps) * w` over rows of the fp32 residual
-stream (`src/core_kernels/rmsnorm.cu:33-84`; the weight multiplies directly)."""
+stream (`src/core_kernels/rmsnorm.cu:33-84`; the weight multiplies directly). With
+`NormSpec.offset` the multiplier is `offset + w` (weights stored around zero); such a norm
+can also complete the stream with a sublayer's normed output on its way (`update`)."""
 
 from __future__ import annotations
 
@@ -17,8 +19,13 @@ class RMSNorm(Part):
     def weight_name(self):
         return self.prefix + getattr(self.spec, "suffix", ".weight")
 
+    @property
+    def offset(self) -> float:
+        return float(getattr(self.spec, "offset", 0.0))
+
     def tensor_decls(self):
-        return [TensorDecl(self.weight_name, (self.spec.size,), init="ones_normal")]
+        return [TensorDecl(self.weight_name, (self.spec.size,),
+                           init="normal" if self.offset else "ones_normal")]
 
     def bind(self, arena):
         self.weight = arena.view(self.weight_name)
@@ -27,11 +34,27 @@ class RMSNorm(Part):
 
     def forward(self, x, out_dtype=None, rows=None, add=None):
         out_dtype = out_dtype or self.act_dtype
+        if self.offset:
+            if add is not None:
+                ops.add_into(x, add)
+            return ops.rms_update(x, out_dtype=out_dtype, out_weight=self.weight,
+                                  out_offset=self.offset, eps=self.spec.eps, rows=rows)
         if add is not None and (rows is not None or out_dtype != torch.bfloat16
                                 or self.weight.dtype != torch.bfloat16):
             ops.add_into(x, add)
             add = None
         return ops.rms_norm(x, self.weight, self.spec.eps, out_dtype, rows, add)
+
+    folds_update = True  # update(x, y, out_dtype) does x += norm(y) and hands the stream on
+
+    def update(self, x, y, out_dtype=None):
+        """`x += norm(y)` in place on the fp32 stream; with `out_dtype`, also returns the
+        completed stream in that type (what a sublayer that reads the stream itself takes)."""
+        return ops.rms_update(x, y, add_weight=self.weight, add_offset=self.offset,
+                              out_dtype=out_dtype, eps=self.spec.eps)
+
+    def complete(self, x, y):
+        self.update(x, y)
 
 
 class LayerNorm(RMSNorm):
@@ -46,6 +69,7 @@ class LayerNorm(RMSNorm):
 
     folds_add = False            # a plain delta is added by `ops.add_into` first
     folds_normed = True
+    folds_update = False
 
     def forward(self, x, out_dtype=None, rows=None, add=None, add_norm=None):
         out_dtype = out_dtype or self.act_dtype

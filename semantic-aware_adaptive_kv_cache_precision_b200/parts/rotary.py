@@ -46,6 +46,15 @@ class RotaryHalf(Part):
         sc = getattr(self.spec, "scaling", None)
         if sc is None:
             return inv_freq, 1.0
+        if hasattr(sc, "low"):
+            # bands of wavelength: short ones stay, long ones turn `factor` times slower, and
+            # between `original / high` and `original / low` the two are blended
+            wavelength = 2.0 * np.pi / inv_freq
+            blend = (sc.original / wavelength - sc.low) / (sc.high - sc.low)
+            mixed = (1.0 - blend) * inv_freq / sc.factor + blend * inv_freq
+            out = np.where(wavelength > sc.original / sc.low, inv_freq / sc.factor,
+                           np.where(wavelength < sc.original / sc.high, inv_freq, mixed))
+            return out, 1.0
 
         def pair_with(turns):
             return rot * np.log(sc.original / (2.0 * np.pi * turns)) / (2.0 * np.log(theta))
