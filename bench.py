@@ -449,6 +449,112 @@ def venanex_rates(size, times, batch, context, tokens, hbm) -> dict:
     return out
 
 
+#: layer sizes for `--design zodirax`: (width, selective scan: inner, state, dt_rank, taps;
+#: window attention heads / kv heads x (dim, vdim) with window and kept first tokens, rotated
+#: numbers a head; fading-state attention heads x (dim, vdim); feed-forward)
+ZODIRAX_SIZES = {
+    "1k": dict(width=1024, scan=(2048, 16, 64, 4), attention=(8, 2, 128, 128), window=512,
+               keep_first=4, rot=64, fading=(16, 64, 64), ff=4096, vocab=32768, layers=6),
+    "2k": dict(width=2048, scan=(4096, 16, 128, 4), attention=(16, 4, 128, 128), window=1024,
+               keep_first=4, rot=64, fading=(32, 64, 64), ff=8192, vocab=32768, layers=6),
+}
+
+
+def zodirax_configs(size: dict) -> tuple:
+    """(Zodirax config, the Tebonex config of equal width, depth, attention heads, window and
+    feed-forward: the library's other design with recurrent layers beside windowed attention)."""
+    heads, kv_heads, dim, vdim = size["attention"]
+    inner, state, dt_rank, taps = size["scan"]
+    fheads, fdim, fvdim = size["fading"]
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    layers, other = [], []
+    for i in range(size["layers"]):
+        if i % 3 == 2:
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+                    "scale": dim ** -0.5,
+                    "mask": {"size": size["window"], "keep_first": size["keep_first"]},
+                    "rot": {"base": 10000.0, "dims": size["rot"],
+                            "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            right = {"heads": fheads, "dim": fdim, "vdim": fvdim,
+                     "decay": [1.0 - 2.0 ** -(2 + 8 * h / fheads) for h in range(fheads)]}
+            layers.append({"type": "parallel", "mlp": mlp,
+                           "mixer": {"left": left, "right": right, "left_scale": 1.0,
+                                     "right_scale": 1.0}})
+            other.append({"type": "attention", "mlp": mlp,
+                          "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+                                    "scale": dim ** -0.5, "mask": {"size": size["window"]}}})
+        else:
+            layers.append({"type": "mamba1", "mlp": mlp,
+                           "mixer": {"inner": inner, "state": state, "dt_rank": dt_rank,
+                                     "conv": taps}})
+            other.append({"type": "general_delta", "mlp": mlp,
+                          "mixer": {"heads": size["width"] // 64, "dim": 64, "decay_rank": 64}})
+    zodirax = {"architecture": "Zodirax", "vocab": size["vocab"], "width": size["width"],
+               "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "initializer_range": 0.02,
+               "layers": layers}
+    tebonex = {"architecture": "Tebonex", "vocab": size["vocab"], "width": size["width"],
+               "streams": 1, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+               "initializer_range": 0.02, "layers": other}
+    return zodirax, tebonex
+
+
+def zodirax_rates(size, zt, tt, batch, context, tokens, hbm) -> dict:
+    """What the recurrent and attention kernels of the two designs must move in the timed steps,
+    as fractions of the measured copy bandwidth (prompts: the activations they read and write;
+    decode steps: the states and cached rows they read and write), and the fp32 multiply-adds
+    of the attention over a prompt. `zt`, `tt`: kernel times of Zodirax and Tebonex."""
+    heads, kv_heads, dim, vdim = size["attention"]
+    inner, state, dt_rank, taps = size["scan"]
+    fheads, fdim, fvdim = size["fading"]
+    n_par = sum(1 for i in range(size["layers"]) if i % 3 == 2)
+    n_scan = size["layers"] - n_par
+    width = size["width"]
+
+    def of_hbm(nbytes, us):
+        return round(nbytes / (us * 1e-6) / 1e9 / hbm, 3) if us else None
+
+    out = {}
+    # the scan over a prompt: x (bf16), dt and z (fp32) in, y (bf16) out a channel, B and C a token
+    moved = tokens * (inner * (2 + 4 + 4 + 2) + 2 * state * 4) * n_scan
+    out["selective_scan_prefill_of_measured_hbm"] = of_hbm(moved, zt["prefill"].get("selective_scan"))
+    moved = batch * (inner * state * 4 * 2 + inner * 12) * n_scan + inner * state * 2 * n_scan
+    out["selective_scan_decode_of_measured_hbm"] = of_hbm(moved, zt["decode"].get("selective_scan"))
+    qkv = fheads * (2 * fdim + fvdim)
+    moved = tokens * (qkv + fheads * fvdim) * 4 * n_par
+    out["decay_attention_prefill_of_measured_hbm"] = of_hbm(moved, zt["prefill"].get("decay_attention"))
+    moved = batch * (fheads * fdim * fvdim * 4 * 2 + (qkv + fheads * fvdim) * 4) * n_par
+    out["decay_attention_decode_of_measured_hbm"] = of_hbm(moved, zt["decode"].get("decay_attention"))
+    keys = sum(min(i + 1, size["window"] + size["keep_first"]) for i in range(tokens))
+    flops = 2.0 * heads * (dim + vdim) * keys * n_par
+    if zt["prefill"].get("cached_attention"):
+        out["attention_prefill_tflops_fp32"] = round(
+            flops / (zt["prefill"]["cached_attention"] * 1e-6) / 1e12, 2)
+    seen = min(context, size["window"] + size["keep_first"])
+    out["attention_decode_of_measured_hbm"] = of_hbm(
+        batch * seen * kv_heads * (dim + vdim) * 2 * n_par, zt["decode"].get("cached_attention"))
+    # between two sublayers: y and x in, x (fp32) and its bf16 copy out
+    moved = tokens * width * (4 + 4 + 4 + 2) * 2 * size["layers"]
+    out["rms_update_prefill_of_measured_hbm"] = of_hbm(moved, zt["prefill"].get("rms_update"))
+    # the like kernels of the other design, in the same run
+    delta_heads = width // 64
+    if tt["prefill"].get("delta_rule"):
+        moved = tokens * delta_heads * 64 * (2 * 4 + 2) * 4 * n_scan       # q, k, v, decays; out
+        out["tebonex_delta_rule_prefill_of_measured_hbm"] = of_hbm(moved, tt["prefill"]["delta_rule"])
+    if tt["decode"].get("delta_rule"):
+        out["tebonex_delta_rule_decode_of_measured_hbm"] = of_hbm(
+            batch * delta_heads * 64 * 64 * 4 * 2 * n_scan, tt["decode"]["delta_rule"])
+    if tt["prefill"].get("distance_attention"):
+        keys = sum(min(i + 1, size["window"]) for i in range(tokens))
+        out["tebonex_attention_prefill_tflops_fp32"] = round(
+            2.0 * heads * (dim + vdim) * keys * n_par
+            / (tt["prefill"]["distance_attention"] * 1e-6) / 1e12, 2)
+    if tt["decode"].get("distance_attention"):
+        out["tebonex_attention_decode_of_measured_hbm"] = of_hbm(
+            batch * min(context, size["window"]) * kv_heads * (dim + vdim) * 2 * n_par,
+            tt["decode"]["distance_attention"])
+    return out
+
+
 def design_configs(size: dict) -> tuple:
     """(Tebonex config, the Qwen2 config of equal width, depth, heads and feed-forward)."""
     heads, kv_heads, dim = size["attention"]
@@ -599,6 +705,35 @@ def design_arm(args) -> int:
                           "batch": batch, "context": context, "prefill_tokens": tokens, "steps": K,
                           "warmup": W, "peaks": pk, "sizes": rows}))
         return 0
+    if args.design == "zodirax":
+        for name in sizes:
+            size = ZODIRAX_SIZES[name]
+            zodirax, tebonex = zodirax_configs(size)
+            row = {"size": name, **{k: size[k] for k in ("width", "layers", "ff", "scan", "window",
+                                                         "attention", "fading")}}
+            kernels = {}
+            for label, config in (("tebonex", tebonex), ("zodirax", zodirax)):
+                engine, slots, prompt, out = measure(config)
+                row[label] = out
+                engine.close(slots)
+                engine.release()
+                del engine
+                torch.cuda.empty_cache()
+                engine, slots, prompt, _ = measure(config, graphs=False)
+                row[label + "_kernels_us"] = kernels[label] = kernel_times(engine, slots, prompt)
+                engine.close(slots)
+                engine.release()
+                del engine
+                torch.cuda.empty_cache()
+            row["kernel_rates"] = zodirax_rates(size, kernels["zodirax"], kernels["tebonex"], batch,
+                                                context, tokens, hbm)
+            rows.append(row)
+        print(json.dumps({"design": "zodirax", "beside": "tebonex of equal width, depth, "
+                          "attention heads, window and feed-forward size, one stream", "dtype": "bf16",
+                          "data": "synthetic (random weights and tokens; weights larger than L2)",
+                          "batch": batch, "context": context, "prefill_tokens": tokens, "steps": K,
+                          "warmup": W, "peaks": pk, "sizes": rows}))
+        return 0
     for name in sizes:
         size = DESIGN_SIZES[name]
         tebonex, qwen2 = design_configs(size)
@@ -655,7 +790,7 @@ def design_arm(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["tebonex", "venanex"],
+    ap.add_argument("--design", default=None, choices=["tebonex", "venanex", "zodirax"],
                     help="instead of the default workload: the named design at layer sizes "
                          "that resemble real models, beside the Qwen2 decoder of equal size")
     ap.add_argument("--design-sizes", default="1k,2k", help="which of: " + ", ".join(DESIGN_SIZES))

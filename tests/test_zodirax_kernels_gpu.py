@@ -166,7 +166,7 @@ def test_keys_at_the_window_s_edge_and_the_kept_first_tokens(dtype, heads, kv_he
             close(got, want[lo:hi], T, f"positions {lo}..{hi}, {across} blocks")
 
     run([(0, n, 1), (0, 3, 1), (0, 1, -2), (keep, keep + 1, -1), (max(keep - 1, 0), keep + 2, 1),
-         (min(keep + w - 2, n - 3), min(keep + w + 1, n), 1)], table)
+         (max(min(keep + w - 2, n - 3), 0), min(keep + w + 1, n), 1)], table)
     # what a running sequence no longer holds: whole blocks behind the asker's window, but for
     # the kept tokens' blocks
     decoded = table.clone()
@@ -212,7 +212,7 @@ def test_a_whole_prompt_under_the_window_and_two_sequences_of_one_step(dtype):
         if dtype == "float32" and first:
             continue
         got = ops.cached_attention(dev(last, T), cache.keys, cache.values, step.positions,
-                                   step.token_seq, table.flip(0).contiguous(), heads, dim, vdim,
+                                   step.token_seq, table, heads, dim, vdim,
                                    scale, window=window, keep_first=keep, sink=dev(sinks),
                                    key_splits=across, heads_first=first)
         close(got, np.stack([wants[1][70], wants[0][199]]), T, "two last tokens")
@@ -278,10 +278,12 @@ def test_selective_scan_over_pieces_with_a_token_far_back(dtype, channels, n_sta
         dt = plain.softplus(low[:, :rank] @ w_dt.T + b_dt)
         y = plain.selective_scan(x, dt, -np.exp(a_log), low[:, rank + 3:rank + 3 + n_state],
                                  low[:, rank + 3 + n_state:], d_skip)
-        if n > 100:
-            held = plain.selective_scan(x[:3], dt[:3], -np.exp(a_log), low[:3, rank + 3:rank + 3 + n_state],
-                                        low[:3, rank + 3 + n_state:], d_skip * 0)
-            assert abs(y[-1, 0]) > 0.1 * np.abs(held[2, 0]) > 1.0           # the far token is felt
+        if n > 100:                                 # the far token is felt at the last one
+            bare = x.copy()
+            bare[2, 0] = 0.0
+            other = plain.selective_scan(bare, dt, -np.exp(a_log), low[:, rank + 3:rank + 3 + n_state],
+                                         low[:, rank + 3 + n_state:], d_skip)
+            assert abs(y[-1, 0] - other[-1, 0]) > 0.05 * np.abs(y[-1]).max()
         seqs.append((x, low, z, dt, y * plain.silu(z)))
     state = torch.full((5, channels, n_state), 3.0, device=DEV)
     for cuts in ((400, 5, 64), (1, 1, 1), (2, 2, 2), (63, 4, 33), (399, 1, 64)):
@@ -345,7 +347,7 @@ def test_fading_state_over_pieces_with_a_token_far_back(heads, dim, vdim, decay)
             for i in range(n):
                 S = decay[h] * S + np.outer(k[i, h], v[i, h])
                 o[i, h] = S.T @ q[i, h]
-        if n > 100:
+        if n > 100 and decay[slow] > 0.999:
             far = decay[slow] ** (n - 2) * (k[1, slow] @ q[-1, slow]) * v[1, slow]
             assert np.abs(far).max() > 0.5 * np.abs(o[-1, slow]).max()
         o = o.reshape(n, vc)
