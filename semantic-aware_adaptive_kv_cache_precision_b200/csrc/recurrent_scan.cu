@@ -75,21 +75,64 @@ __global__ void conv_state_kernel(const float* __restrict__ in, long long stride
 }
 
 // ---------------------------------------------------------------------------------------
-// Step sizes: dt[t, c] = softplus(sum_r low[t, r] Wdt[c, r] + b[c]). A block a token.
+// Step sizes: dt[t, c] = softplus(sum_r low[t, r] Wdt[c, r] + b[c]), a tiled fp32 product
+// (plain FFMA): a block of 256 threads makes BM tokens x 64 channels, a thread TM x 4 of
+// them, both operands staged through shared memory 16 numbers of the sum at a time. Every
+// output adds its products in the order r = 0, 1, 2, ... whatever the tile.
 // ---------------------------------------------------------------------------------------
-template <typename W>
-__global__ void step_size_kernel(const float* __restrict__ low, long long stride, int rank,
-                                 const W* __restrict__ w, const W* __restrict__ bias,
-                                 float* __restrict__ dt, int channels) {
-  extern __shared__ float row[];
-  const long long t = blockIdx.x;
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) row[r] = low[t * stride + r];
-  __syncthreads();
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-    const W* wr = w + (long long)c * rank;
-    float acc = 0.f;
-    for (int r = 0; r < rank; ++r) acc = fmaf(row[r], widen(wr[r]), acc);
-    dt[t * channels + c] = softplus(acc + (bias ? widen(bias[c]) : 0.f));
+constexpr int kStepN = 64, kStepK = 16;
+
+template <int BM, typename W>
+__global__ void __launch_bounds__(256)
+step_size_kernel(const float* __restrict__ low, long long stride, int rank,
+                 const W* __restrict__ w, const W* __restrict__ bias, float* __restrict__ dt,
+                 int tokens, int channels) {
+  constexpr int TM = BM / 16;
+  __shared__ float As[kStepK][BM + 4];
+  __shared__ float Ws[kStepK][kStepN + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * kStepN;
+  float acc[TM][4];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < rank; k0 += kStepK) {
+    for (int i = threadIdx.x; i < BM * kStepK; i += 256) {
+      const int r = i / kStepK, c = i % kStepK;
+      const int m = m0 + r, k = k0 + c;
+      As[c][r] = (m < tokens && k < rank) ? low[(long long)m * stride + k] : 0.f;
+    }
+    for (int i = threadIdx.x; i < kStepN * kStepK; i += 256) {
+      const int r = i / kStepK, c = i % kStepK;
+      const int n = n0 + r, k = k0 + c;
+      Ws[c][r] = (n < channels && k < rank) ? widen(w[(long long)n * rank + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kStepK; ++k) {
+      float a[TM], b[4];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[k][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int m = m0 + ty * TM + i;
+    if (m >= tokens) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < channels)
+        dt[(long long)m * channels + n] = softplus(acc[i][j] + (bias ? widen(bias[n]) : 0.f));
+    }
   }
 }
 
@@ -98,8 +141,16 @@ __global__ void step_size_kernel(const float* __restrict__ low, long long stride
 // (state n = g * NPT + k belongs to lane g); a lane keeps its states in registers for the
 // whole step, the sum over the states ends with log2(G) shuffles. Blocks: (channels * G /
 // blockDim, sequences). State in memory: [slots, channels, N].
+//
+// A long prompt is cut into runs of `chunk_len` tokens that are walked side by side, in
+// three launches. PHASE 1: every run starts from zero and leaves its end state and the sum of
+// its step sizes in scratch memory ([sequences, max_chunks, channels, N] and [..., channels]).
+// The carry kernel then walks a sequence's runs in order: the state a run starts from replaces
+// what the run left, S <- exp(A sum dt) S + left. PHASE 2: every run starts from there and
+// writes its outputs. PHASE 0 is the whole step by one walk (the sums then do not depend on
+// how a sequence was cut into steps).
 // ---------------------------------------------------------------------------------------
-template <int NPT, typename W, typename C>
+template <int NPT, int PHASE, typename W, typename C>
 __global__ void selective_scan_kernel(const C* __restrict__ x, const float* __restrict__ dt,
                                       const float* __restrict__ low, long long low_stride,
                                       int b_off, int c_off, const float* __restrict__ z,
@@ -107,49 +158,93 @@ __global__ void selective_scan_kernel(const C* __restrict__ x, const float* __re
                                       const W* __restrict__ d_skip, float* __restrict__ state,
                                       const int32_t* __restrict__ cu_seqlens,
                                       const int32_t* __restrict__ slots, C* __restrict__ out,
-                                      int channels, int n_state, int lanes, int keep_state) {
-  const int b = blockIdx.y;
+                                      int channels, int n_state, int lanes, int keep_state,
+                                      int chunk_len, int max_chunks, float* __restrict__ scratch,
+                                      float* __restrict__ dt_sums) {
+  const int b = PHASE == 0 ? blockIdx.y : blockIdx.y / max_chunks;
+  const int run = PHASE == 0 ? 0 : blockIdx.y % max_chunks;
+  int first = cu_seqlens[b], last = cu_seqlens[b + 1];
+  if (PHASE != 0) {
+    first += run * chunk_len;
+    if (first >= last) return;                        // (the whole block: b and run are its own)
+    if (last - first > chunk_len) last = first + chunk_len;
+  }
   const long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   const int c_raw = static_cast<int>(id / lanes), g = static_cast<int>(id % lanes);
   const bool live = c_raw < channels;                 // (idle lanes still join the shuffles)
   const int c = live ? c_raw : channels - 1;
   const int n0 = g * NPT;
   float a[NPT], s[NPT];
-  float* mine = state + ((long long)slots[b] * channels + c) * n_state + n0;
+  float* mine = PHASE == 0
+                    ? state + ((long long)slots[b] * channels + c) * n_state + n0
+                    : scratch + (((long long)b * max_chunks + run) * channels + c) * n_state + n0;
 #pragma unroll
   for (int k = 0; k < NPT; ++k) {
     const bool has = n0 + k < n_state;
     a[k] = has ? -expf(widen(a_log[(long long)c * n_state + n0 + k])) : 0.f;
-    s[k] = has ? mine[k] : 0.f;
+    s[k] = (has && PHASE != 1) ? mine[k] : 0.f;
   }
   const float skip = widen(d_skip[c]);
-  const int first = cu_seqlens[b], last = cu_seqlens[b + 1];
+  float dt_sum = 0.f;
   for (int t = first; t < last; ++t) {
     const float step = dt[(long long)t * channels + c];
     const float xv = widen(x[(long long)t * channels + c]);
     const float* bt = low + (long long)t * low_stride + b_off + n0;
     const float* ct = low + (long long)t * low_stride + c_off + n0;
     const float dx = step * xv;
+    dt_sum += step;
     float y = 0.f;
 #pragma unroll
     for (int k = 0; k < NPT; ++k) {
       const bool has = n0 + k < n_state;
-      const float bv = has ? bt[k] : 0.f, cv = has ? ct[k] : 0.f;
+      const float bv = has ? bt[k] : 0.f;
       // S + (e^(dt A) - 1) S + dt x B: a decay close to 1 keeps its distance from 1 exactly
       s[k] += fmaf(expm1f(step * a[k]), s[k], dx * bv);
-      y = fmaf(s[k], cv, y);
+      if (PHASE != 1) y = fmaf(s[k], has ? ct[k] : 0.f, y);
     }
-    for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-    if (g == 0 && live) {
-      y = fmaf(skip, xv, y);
-      out[(long long)t * channels + c] = narrow<C>(y * silu(z[(long long)t * z_stride + c]));
+    if (PHASE != 1) {
+      for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (g == 0 && live) {
+        y = fmaf(skip, xv, y);
+        out[(long long)t * channels + c] = narrow<C>(y * silu(z[(long long)t * z_stride + c]));
+      }
     }
   }
-  if (keep_state && live) {
+  if (live && (PHASE == 1 || (PHASE == 0 && keep_state))) {
 #pragma unroll
     for (int k = 0; k < NPT; ++k)
       if (n0 + k < n_state) mine[k] = s[k];
   }
+  if (PHASE == 1 && live && g == 0)
+    dt_sums[((long long)b * max_chunks + run) * channels + c] = dt_sum;
+}
+
+// Between the two passes over a prompt's runs: one thread a (sequence, channel, state) walks
+// the runs in order. What a run left (its end state from zero) is replaced by the state it
+// starts from; the state after the last run goes back to the sequence's slot.
+template <typename W>
+__global__ void scan_carry_kernel(const W* __restrict__ a_log, float* __restrict__ state,
+                                  float* __restrict__ scratch, const float* __restrict__ dt_sums,
+                                  const int32_t* __restrict__ cu_seqlens,
+                                  const int32_t* __restrict__ slots, int sequences, int channels,
+                                  int n_state, int chunk_len, int max_chunks, int keep_state) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long per = (long long)channels * n_state;
+  if (idx >= sequences * per) return;
+  const int b = static_cast<int>(idx / per);
+  const long long cn = idx - b * per;
+  const int c = static_cast<int>(cn / n_state);
+  const int runs = (cu_seqlens[b + 1] - cu_seqlens[b] + chunk_len - 1) / chunk_len;
+  const float a = -expf(widen(a_log[cn]));
+  float* home = state + (long long)slots[b] * per + cn;
+  float s = *home;
+  for (int j = 0; j < runs; ++j) {
+    float* p = scratch + ((long long)b * max_chunks + j) * per + cn;
+    const float left = *p;
+    *p = s;
+    s += fmaf(expm1f(a * dt_sums[((long long)b * max_chunks + j) * channels + c]), s, left);
+  }
+  if (keep_state) *home = s;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -162,7 +257,11 @@ __global__ void selective_scan_kernel(const C* __restrict__ x, const float* __re
 // ---------------------------------------------------------------------------------------
 constexpr int kRun = 16;          // tokens brought into shared memory at a time
 
-template <int RP>
+// PHASE as in the selective scan: 0 walks a sequence's whole part of the step from the state in
+// its slot; 1 walks one run of `chunk_len` tokens from zero and leaves the end state in scratch
+// memory ([sequences, max_chunks, heads, vdim, dim]), without outputs; 2 walks a run from the
+// state that the carry kernel put there and writes the outputs.
+template <int RP, int PHASE>
 __global__ void decay_attention_kernel(const float* __restrict__ proj, long long stride,
                                        int q_off, int k_off, int v_off,
                                        const float* __restrict__ decay_less_one,
@@ -170,29 +269,40 @@ __global__ void decay_attention_kernel(const float* __restrict__ proj, long long
                                        const int32_t* __restrict__ cu_seqlens,
                                        const int32_t* __restrict__ slots, float* __restrict__ out,
                                        int heads, int dim, int vdim, int rs, int cols,
-                                       int keep_state) {
+                                       int keep_state, int chunk_len, int max_chunks,
+                                       float* __restrict__ scratch) {
   extern __shared__ __align__(16) float shared[];
   const int padded = rs * RP;                       // dim rounded up to whole lanes
   float* qs = shared;                               // [kRun, padded]
   float* ks = qs + kRun * padded;                   // [kRun, padded]
   float* vs = ks + kRun * padded;                   // [kRun, cols]
-  const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * cols;
+  const int b = PHASE == 0 ? blockIdx.z : blockIdx.z / max_chunks;
+  const int piece = PHASE == 0 ? 0 : blockIdx.z % max_chunks;
+  int first = cu_seqlens[b], last = cu_seqlens[b + 1];
+  if (PHASE != 0) {
+    first += piece * chunk_len;
+    if (first >= last) return;                      // (the whole block)
+    if (last - first > chunk_len) last = first + chunk_len;
+  }
+  const int h = blockIdx.y, col0 = blockIdx.x * cols;
   const int r = threadIdx.x % rs, j = threadIdx.x / rs;
   const int col = col0 + j;
   const bool live = col < vdim;
   const float fade = decay_less_one[h];        // decay - 1, rounded once from the exact number
   float s[RP];
-  float* mine = state + (((long long)slots[b] * heads + h) * vdim + (live ? col : 0)) * dim + r * RP;
+  const long long place = ((long long)h * vdim + (live ? col : 0)) * dim + r * RP;
+  float* mine = PHASE == 0
+                    ? state + (long long)slots[b] * heads * vdim * dim + place
+                    : scratch + ((long long)b * max_chunks + piece) * heads * vdim * dim + place;
 #pragma unroll
-  for (int k = 0; k < RP; ++k) s[k] = (live && r * RP + k < dim) ? mine[k] : 0.f;
-  const int first = cu_seqlens[b], last = cu_seqlens[b + 1];
+  for (int k = 0; k < RP; ++k) s[k] = (PHASE != 1 && live && r * RP + k < dim) ? mine[k] : 0.f;
   for (int t0 = first; t0 < last; t0 += kRun) {
     const int run = last - t0 < kRun ? last - t0 : kRun;
     __syncthreads();
     for (int e = threadIdx.x; e < run * padded; e += blockDim.x) {
       const int tt = e / padded, i = e - tt * padded;
       const float* row = proj + (long long)(t0 + tt) * stride + (long long)h * dim + i;
-      qs[e] = i < dim ? silu(row[q_off]) : 0.f;
+      if (PHASE != 1) qs[e] = i < dim ? silu(row[q_off]) : 0.f;
       ks[e] = i < dim ? silu(row[k_off]) : 0.f;
     }
     for (int e = threadIdx.x; e < run * cols; e += blockDim.x) {
@@ -208,17 +318,47 @@ __global__ void decay_attention_kernel(const float* __restrict__ proj, long long
 #pragma unroll
       for (int k = 0; k < RP; ++k) {
         s[k] += fmaf(fade, s[k], ks[tt * padded + r * RP + k] * v);
-        o = fmaf(s[k], qs[tt * padded + r * RP + k], o);
+        if (PHASE != 1) o = fmaf(s[k], qs[tt * padded + r * RP + k], o);
       }
-      for (int d = rs >> 1; d > 0; d >>= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
-      if (r == 0 && live) out[((long long)(t0 + tt) * heads + h) * vdim + col] = o;
+      if (PHASE != 1) {
+        for (int d = rs >> 1; d > 0; d >>= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
+        if (r == 0 && live) out[((long long)(t0 + tt) * heads + h) * vdim + col] = o;
+      }
     }
   }
-  if (keep_state && live) {
+  if (live && (PHASE == 1 || (PHASE == 0 && keep_state))) {
 #pragma unroll
     for (int k = 0; k < RP; ++k)
       if (r * RP + k < dim) mine[k] = s[k];
   }
+}
+
+// Between the two passes over a prompt's runs: one thread a (sequence, head, column, row) walks
+// the runs in order; a run of n tokens fades what came before by decay^n.
+__global__ void decay_carry_kernel(const float* __restrict__ decay_less_one,
+                                   float* __restrict__ state, float* __restrict__ scratch,
+                                   const int32_t* __restrict__ cu_seqlens,
+                                   const int32_t* __restrict__ slots, int sequences, int heads,
+                                   long long per_head, int chunk_len, int max_chunks,
+                                   int keep_state) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long per = heads * per_head;
+  if (idx >= sequences * per) return;
+  const int b = static_cast<int>(idx / per);
+  const long long e = idx - b * per;
+  const int n = cu_seqlens[b + 1] - cu_seqlens[b];
+  const int runs = (n + chunk_len - 1) / chunk_len;
+  const float log_fade = log1pf(decay_less_one[e / per_head]);
+  float* home = state + (long long)slots[b] * per + e;
+  float s = *home;
+  for (int j = 0; j < runs; ++j) {
+    float* p = scratch + ((long long)b * max_chunks + j) * per + e;
+    const float left = *p;
+    *p = s;
+    const int len = n - j * chunk_len < chunk_len ? n - j * chunk_len : chunk_len;
+    s += fmaf(expm1f(log_fade * static_cast<float>(len)), s, left);
+  }
+  if (keep_state) *home = s;
 }
 
 // out[t] = y[t] / sqrt(mean(y[t]^2) + eps) * w * sigmoid(gate[t]) * scale over the whole row
@@ -289,16 +429,23 @@ SAKV_EXPORT int sakv_conv_state(const float* in, long long stride, float* state,
 SAKV_EXPORT int sakv_step_size(const float* low, long long stride, int rank, const void* w,
                                const void* bias, int w_dtype, float* dt, int tokens, int channels,
                                cudaStream_t stream) {
-  if (tokens < 0 || channels <= 0 || rank <= 0 || rank > 8192) return cudaErrorInvalidValue;
+  if (tokens < 0 || channels <= 0 || rank <= 0) return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
-  const size_t smem = (size_t)rank * sizeof(float);
-  if (w_dtype == SAKV_F32)
-    return launch_ordered(step_size_kernel<float>, dim3(tokens), dim3(256), smem, stream, low,
-                          stride, rank, (const float*)w, (const float*)bias, dt, channels);
-  if (w_dtype == SAKV_BF16)
-    return launch_ordered(step_size_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), smem, stream,
-                          low, stride, rank, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias,
-                          dt, channels);
+  const bool few = tokens <= 16;
+  const dim3 grid((unsigned)((channels + kStepN - 1) / kStepN),
+                  (unsigned)((tokens + (few ? 15 : 63)) / (few ? 16 : 64)));
+#define SAKV_STEP(BM, W)                                                                         \
+  return launch_ordered(step_size_kernel<BM, W>, grid, dim3(256), 0, stream, low, stride, rank,  \
+                        (const W*)w, (const W*)bias, dt, tokens, channels)
+  if (w_dtype == SAKV_F32) {
+    if (few) SAKV_STEP(16, float);
+    SAKV_STEP(64, float);
+  }
+  if (w_dtype == SAKV_BF16) {
+    if (few) SAKV_STEP(16, __nv_bfloat16);
+    SAKV_STEP(64, __nv_bfloat16);
+  }
+#undef SAKV_STEP
   return cudaErrorInvalidValue;
 }
 
@@ -312,33 +459,54 @@ SAKV_EXPORT int sakv_selective_scan(const void* x, int c_dtype, const float* dt,
                                     long long z_stride, const void* a_log, const void* d_skip,
                                     int w_dtype, float* state, const int32_t* cu_seqlens,
                                     const int32_t* slots, void* out, int tokens, int sequences,
-                                    int channels, int n_state, int keep_state,
+                                    int channels, int n_state, int keep_state, int chunk_len,
+                                    int max_chunks, float* scratch, float* dt_sums,
                                     cudaStream_t stream) {
   if (tokens < 0 || sequences < 0 || channels <= 0 || n_state <= 0 || n_state > 512)
     return cudaErrorInvalidValue;
   if (tokens == 0 || sequences == 0) return 0;
+  const bool runs = chunk_len > 0;
+  if (runs && (max_chunks <= 0 || scratch == nullptr || dt_sums == nullptr ||
+               (long long)sequences * max_chunks > 65535))
+    return cudaErrorInvalidValue;
   const int per_lane = n_state <= 128 ? 4 : 16;
   const int lanes = lanes_for(n_state, per_lane);
   const long long threads = (long long)channels * lanes;
-  // smaller blocks while the step's sequences and channels do not fill the GPU
+  const long long walks = runs ? (long long)sequences * max_chunks : sequences;
+  // smaller blocks while the step's walks and channels do not fill the GPU
   int block = 128;
-  while (block > 32 && (threads + block - 1) / block * sequences < 2LL * sm_count()) block /= 2;
-  const dim3 grid((unsigned)((threads + block - 1) / block), (unsigned)sequences);
-#define SAKV_SCAN(NPT, W, C)                                                                     \
-  return launch_ordered(selective_scan_kernel<NPT, W, C>, grid, dim3(block), 0, stream,          \
-                        (const C*)x, dt, low, low_stride, b_off, c_off, z, z_stride,             \
-                        (const W*)a_log, (const W*)d_skip, state, cu_seqlens, slots, (C*)out,    \
-                        channels, n_state, lanes, keep_state)
+  while (block > 32 && (threads + block - 1) / block * walks < 2LL * sm_count()) block /= 2;
+  const dim3 grid((unsigned)((threads + block - 1) / block), (unsigned)walks);
+#define SAKV_SCAN(NPT, PHASE, W, C)                                                              \
+  launch_ordered(selective_scan_kernel<NPT, PHASE, W, C>, grid, dim3(block), 0, stream,          \
+                 (const C*)x, dt, low, low_stride, b_off, c_off, z, z_stride, (const W*)a_log,   \
+                 (const W*)d_skip, state, cu_seqlens, slots, (C*)out, channels, n_state, lanes,  \
+                 keep_state, chunk_len, max_chunks, scratch, dt_sums)
+#define SAKV_SCAN_ALL(NPT, W, C)                                                                 \
+  do {                                                                                           \
+    if (!runs) return SAKV_SCAN(NPT, 0, W, C);                                                   \
+    int code = SAKV_SCAN(NPT, 1, W, C);                                                          \
+    if (code) return code;                                                                       \
+    const long long count = (long long)sequences * channels * n_state;                           \
+    code = launch_ordered(scan_carry_kernel<W>, dim3((unsigned)((count + 127) / 128)),           \
+                          dim3(128), 0, stream, (const W*)a_log, state, scratch, dt_sums,        \
+                          cu_seqlens, slots, sequences, channels, n_state, chunk_len,            \
+                          max_chunks, keep_state);                                               \
+    if (code) return code;                                                                       \
+    return SAKV_SCAN(NPT, 2, W, C);                                                              \
+  } while (0)
 #define SAKV_SCAN_T(NPT)                                                                         \
   do {                                                                                           \
-    if (w_dtype == SAKV_F32 && c_dtype == SAKV_F32) SAKV_SCAN(NPT, float, float);                \
-    if (w_dtype == SAKV_BF16 && c_dtype == SAKV_BF16) SAKV_SCAN(NPT, __nv_bfloat16, __nv_bfloat16); \
-    if (w_dtype == SAKV_F32 && c_dtype == SAKV_BF16) SAKV_SCAN(NPT, float, __nv_bfloat16);       \
-    if (w_dtype == SAKV_BF16 && c_dtype == SAKV_F32) SAKV_SCAN(NPT, __nv_bfloat16, float);       \
+    if (w_dtype == SAKV_F32 && c_dtype == SAKV_F32) SAKV_SCAN_ALL(NPT, float, float);            \
+    if (w_dtype == SAKV_BF16 && c_dtype == SAKV_BF16)                                            \
+      SAKV_SCAN_ALL(NPT, __nv_bfloat16, __nv_bfloat16);                                          \
+    if (w_dtype == SAKV_F32 && c_dtype == SAKV_BF16) SAKV_SCAN_ALL(NPT, float, __nv_bfloat16);   \
+    if (w_dtype == SAKV_BF16 && c_dtype == SAKV_F32) SAKV_SCAN_ALL(NPT, __nv_bfloat16, float);   \
   } while (0)
   if (per_lane == 4) SAKV_SCAN_T(4);
   else SAKV_SCAN_T(16);
 #undef SAKV_SCAN_T
+#undef SAKV_SCAN_ALL
 #undef SAKV_SCAN
   return cudaErrorInvalidValue;
 }
@@ -352,27 +520,47 @@ SAKV_EXPORT int sakv_decay_attention(const float* proj, long long stride, int q_
                                      int v_off, const float* decay, float* state,
                                      const int32_t* cu_seqlens, const int32_t* slots, float* out,
                                      int tokens, int sequences, int heads, int dim, int vdim,
-                                     int keep_state, cudaStream_t stream) {
+                                     int keep_state, int chunk_len, int max_chunks, float* scratch,
+                                     cudaStream_t stream) {
   if (tokens < 0 || sequences < 0 || heads <= 0 || dim <= 0 || dim > 256 || vdim <= 0)
     return cudaErrorInvalidValue;
   if (tokens == 0 || sequences == 0) return 0;
+  const bool runs = chunk_len > 0;
+  if (runs && (max_chunks <= 0 || scratch == nullptr ||
+               (long long)sequences * max_chunks > 65535))
+    return cudaErrorInvalidValue;
+  const long long walks = runs ? (long long)sequences * max_chunks : sequences;
   const int rp = dim <= 128 ? 4 : 8;
   const int rs = lanes_for(dim, rp);
   int cols = 256 / rs;                       // value columns a block
-  // fewer columns a block while the step's heads and sequences do not fill the GPU
-  while (cols > 1 && (long long)((vdim + cols - 1) / cols) * heads * sequences < 2LL * sm_count())
+  // fewer columns a block while the step's heads and walks do not fill the GPU
+  while (cols > 1 && (long long)((vdim + cols - 1) / cols) * heads * walks < 2LL * sm_count())
     cols /= 2;
   while (cols > 1 && cols / 2 >= vdim) cols /= 2;
   if (cols * rs < 32) cols = 32 / rs;        // whole warps
-  const dim3 grid((unsigned)((vdim + cols - 1) / cols), (unsigned)heads, (unsigned)sequences);
+  const dim3 grid((unsigned)((vdim + cols - 1) / cols), (unsigned)heads, (unsigned)walks);
   const size_t smem = (size_t)kRun * (2 * rs * rp + cols) * sizeof(float);
-  if (rp == 4)
-    return launch_ordered(decay_attention_kernel<4>, grid, dim3(cols * rs), smem, stream, proj,
-                          stride, q_off, k_off, v_off, decay, state, cu_seqlens, slots, out, heads,
-                          dim, vdim, rs, cols, keep_state);
-  return launch_ordered(decay_attention_kernel<8>, grid, dim3(cols * rs), smem, stream, proj,
-                        stride, q_off, k_off, v_off, decay, state, cu_seqlens, slots, out, heads,
-                        dim, vdim, rs, cols, keep_state);
+#define SAKV_FADE(RP, PHASE)                                                                     \
+  launch_ordered(decay_attention_kernel<RP, PHASE>, grid, dim3(cols * rs), smem, stream, proj,   \
+                 stride, q_off, k_off, v_off, decay, state, cu_seqlens, slots, out, heads, dim,  \
+                 vdim, rs, cols, keep_state, chunk_len, max_chunks, scratch)
+#define SAKV_FADE_ALL(RP)                                                                        \
+  do {                                                                                           \
+    if (!runs) return SAKV_FADE(RP, 0);                                                          \
+    int code = SAKV_FADE(RP, 1);                                                                 \
+    if (code) return code;                                                                       \
+    const long long per_head = (long long)vdim * dim;                                            \
+    const long long count = (long long)sequences * heads * per_head;                             \
+    code = launch_ordered(decay_carry_kernel, dim3((unsigned)((count + 127) / 128)), dim3(128),  \
+                          0, stream, decay, state, scratch, cu_seqlens, slots, sequences, heads, \
+                          per_head, chunk_len, max_chunks, keep_state);                          \
+    if (code) return code;                                                                       \
+    return SAKV_FADE(RP, 2);                                                                     \
+  } while (0)
+  if (rp == 4) SAKV_FADE_ALL(4);
+  SAKV_FADE_ALL(8);
+#undef SAKV_FADE_ALL
+#undef SAKV_FADE
 }
 
 // y: fp32 [tokens, width]; w: [width] of `w_dtype`; gate: fp32 rows `gate_stride` apart (null:

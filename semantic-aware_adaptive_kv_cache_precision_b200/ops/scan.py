@@ -59,12 +59,18 @@ def step_size(low: torch.Tensor, rank: int, weight: torch.Tensor,
 
 def selective_scan(x: torch.Tensor, dt: torch.Tensor, low: torch.Tensor, b_off: int, c_off: int,
                    n_state: int, z: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
-                   state: torch.Tensor, step, keep_state: bool = True) -> torch.Tensor:
+                   state: torch.Tensor, step, keep_state: bool = True,
+                   run: int = 0) -> torch.Tensor:
     """`S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n; y_c = sum_n S[c, n] C_n + D_c x_c`
     over each sequence's tokens, A = -exp(a_log); returns `y * silu(z)` [T, channels] of x's
     type. `x`: [T, channels]; `dt`: fp32 [T, channels]; B and C: `n_state` columns of fp32
     `low` from `b_off` and `c_off`; `z`: fp32 [T, channels] (a view with any row stride);
-    `state`: fp32 [slots, channels, n_state], read and (with `keep_state`) left."""
+    `state`: fp32 [slots, channels, n_state], read and (with `keep_state`) left.
+
+    `run` 0: one walk over each sequence's tokens, so the sums do not depend on how a sequence
+    was cut into steps. `run` r > 0: a sequence's tokens are walked in runs of r side by side
+    (three launches: the runs from zero, the states carried from run to run, the runs again
+    with their outputs); `step.max_new` bounds a sequence's tokens."""
     require_cuda(x, dt, low, z, a_log, d_skip, state)
     tokens, channels = x.shape
     _check(x.is_contiguous() and dt.dtype == torch.float32 and dt.is_contiguous()
@@ -80,21 +86,37 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, low: torch.Tensor, b_off: 
     _check(state.dtype == torch.float32 and state.is_contiguous()
            and tuple(state.shape[1:]) == (channels, n_state), "state: fp32 [slots, channels, n_state]")
     out = torch.empty_like(x)
+    runs, scratch, sums = _runs(run, step, channels * n_state, channels, x.device)
     call("sakv_selective_scan", ptr(x), dtype_code(x.dtype), ptr(dt), ptr(low), low.stride(0),
          int(b_off), int(c_off), ptr(z), z.stride(0), ptr(a_log), ptr(d_skip),
          dtype_code(a_log.dtype), ptr(state), ptr(step.cu_seqlens), ptr(step.slots), ptr(out),
-         tokens, step.sequences, channels, n_state, int(keep_state))
+         tokens, step.sequences, channels, n_state, int(keep_state), int(run) if runs else 0,
+         runs, ptr(scratch), ptr(sums))
     return out
+
+
+def _runs(run: int, step, state_size: int, sum_size: int, device):
+    """(runs a sequence at most, scratch for every run's state, scratch for its sums) of a
+    step walked in runs of `run` tokens; (0, None, None) where one walk does."""
+    if not run:
+        return 0, None, None
+    runs = -(-int(step.max_new) // int(run))
+    if runs <= 1 or step.sequences * runs > 65535:
+        return 0, None, None
+    scratch = torch.empty((step.sequences * runs, state_size), dtype=torch.float32, device=device)
+    sums = torch.empty((step.sequences * runs, sum_size), dtype=torch.float32,
+                       device=device) if sum_size else None
+    return runs, scratch, sums
 
 
 def decay_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, dim: int,
                     vdim: int, decay_less_one: torch.Tensor, state: torch.Tensor, step,
-                    keep_state: bool = True) -> torch.Tensor:
+                    keep_state: bool = True, run: int = 0) -> torch.Tensor:
     """`S <- decay[h] S + k v^T; o = S^T q` a head over each sequence's tokens, with q, k, v =
     silu of the columns of fp32 `proj` from `q_off`, `k_off` (heads * dim each) and `v_off`
     (heads * vdim). `decay_less_one`: fp32 [heads] holding `decay - 1` (the kernel adds `(decay - 1) S + k
     v^T` to S). `state`: fp32 [slots, heads, vdim, dim] (the state's transpose), read and (with
-    `keep_state`) left. Returns fp32 [T, heads * vdim]."""
+    `keep_state`) left. `run`: as in `selective_scan`. Returns fp32 [T, heads * vdim]."""
     require_cuda(proj, decay_less_one, state)
     tokens = proj.shape[0]
     _check(proj.dtype == torch.float32 and proj.dim() == 2 and proj.stride(1) == 1
@@ -105,9 +127,11 @@ def decay_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, head
     _check(state.dtype == torch.float32 and state.is_contiguous()
            and tuple(state.shape[1:]) == (heads, vdim, dim), "state: fp32 [slots, heads, vdim, dim]")
     out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
+    runs, scratch, _ = _runs(run, step, heads * vdim * dim, 0, proj.device)
     call("sakv_decay_attention", ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off),
          ptr(decay_less_one), ptr(state), ptr(step.cu_seqlens), ptr(step.slots), ptr(out), tokens,
-         step.sequences, heads, dim, vdim, int(keep_state))
+         step.sequences, heads, dim, vdim, int(keep_state), int(run) if runs else 0, runs,
+         ptr(scratch))
     return out
 
 

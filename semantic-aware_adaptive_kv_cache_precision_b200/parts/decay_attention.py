@@ -22,6 +22,10 @@ from ..weights.decl import TensorDecl
 from .base import Part, register_part
 
 
+#: tokens a run when a long prompt is walked in runs side by side
+RUN = 64
+
+
 class DecayAttention(Part):
     kernel_libraries = ("recurrent_scan", "gemm_f32", "gemm_tc")
 
@@ -74,7 +78,8 @@ class DecayAttention(Part):
         s = self.spec
         k_off, v_off = offset + self.qk_cols, offset + 2 * self.qk_cols
         y = ops.decay_attention(proj, offset, k_off, v_off, s.heads, s.head_dim, s.value_dim,
-                                self.decay_less_one, view.state, step, keep_state=write_cache)
+                                self.decay_less_one, view.state, step, keep_state=write_cache,
+                                run=self._run(step))
         gate = proj[:, v_off + self.v_cols:v_off + 2 * self.v_cols] if s.gate else None
         return ops.norm_gate(y, self.norm_w, gate, s.eps, s.out_scale, self.act_dtype)
 
@@ -89,6 +94,14 @@ class DecayAttention(Part):
         if self.w_in is None:
             self.w_in = torch.cat([arena.view(p + n) for n, _ in self._inputs()])
         self.bind_rest(arena)
+
+    def _run(self, step) -> int:
+        """Tokens a run of a long prompt: in bfloat16 a sequence's part of the step is walked
+        in runs side by side (the states carried between them in fp32). In the 32-bit mode,
+        and for short parts, one walk, whose sums do not depend on how the sequence was cut."""
+        if self.act_dtype == torch.float32 or getattr(step, "max_new", 0) < 4 * RUN:
+            return 0
+        return RUN
 
     def cache_need(self):
         s = self.spec

@@ -22,6 +22,10 @@ from ..weights.decl import TensorDecl
 from .base import Part, register_part
 
 
+#: tokens a run when a long prompt is walked in runs side by side
+RUN = 64
+
+
 class SelectiveScanMixer(Part):
     kernel_libraries = ("recurrent_scan", "gemm_f32", "gemm_tc")
 
@@ -49,6 +53,14 @@ class SelectiveScanMixer(Part):
         self.w_dt, self.b_dt = arena.view(p + "dt"), arena.view(p + "dt.b")
         self.a_log, self.d_skip = arena.view(p + "A_log"), arena.view(p + "D")
 
+    def _run(self, step) -> int:
+        """Tokens a run of a long prompt: in bfloat16 a sequence's part of the step is walked
+        in runs side by side (the states carried between them in fp32). In the 32-bit mode,
+        and for short parts, one walk, whose sums do not depend on how the sequence was cut."""
+        if self.act_dtype == torch.float32 or getattr(step, "max_new", 0) < 4 * RUN:
+            return 0
+        return RUN
+
     def cache_need(self):
         s = self.spec
         return MultiNeed((StateNeed((s.taps - 1, s.inner), "float32"),
@@ -65,7 +77,7 @@ class SelectiveScanMixer(Part):
         dt = ops.step_size(low, s.dt_rank, self.w_dt, self.b_dt)
         y = ops.selective_scan(x, dt, low, s.dt_rank, s.dt_rank + s.state, s.state,
                                xz[:, s.inner:], self.a_log, self.d_skip, scan_view.state, step,
-                               keep_state=write_cache)
+                               keep_state=write_cache, run=self._run(step))
         return ops.linear(y, self.w_o, out_dtype=torch.float32)
 
     def forward(self, h, step, view, residual, write_cache=True):

@@ -101,6 +101,24 @@ def test_pieces_of_a_prompt_and_tokens_one_by_one(name, dtype, folders):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(CONFIGS))
+def test_a_long_prompt_whole_in_halves_and_beside_a_short_one(name, dtype, folders):
+    """Long enough that the recurrent layers walk it in runs side by side (in bfloat16)."""
+    engine, config, tensors = setup(folders, name, dtype, max_tokens=2048)
+    p, short = prompts_of(name, (610, 30), seed=8)
+    want = plain.forward(config, tensors, p)
+    whole = engine.forward(p)
+    compare(whole, want, dtype, f"{name}: 610 tokens")
+    slots = engine.open(2)
+    first = engine.step(slots, [p[:321], short], [list(range(321)), list(range(30))]).cpu().numpy()
+    rest = engine.step(slots[:1], [p[321:]], [list(range(289))]).cpu().numpy()
+    engine.close(slots)
+    compare(np.concatenate([first[:321], rest]), whole, dtype, f"{name}: in two steps", same=True)
+    compare(first[321:], plain.forward(config, tensors, short), dtype, f"{name}: the short one")
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
 def test_unequal_batches_with_slots_blocks_and_states_used_again(name, dtype, folders):
     """The cache holds exactly one batch, so every batch gets blocks and slots that the batch
     before gave back (blocks filled with NaN when they were freed, states left as they were:

@@ -23,7 +23,7 @@ def scan_step(lengths, slots):
     cu = np.concatenate([[0], np.cumsum(lengths)])
     return SimpleNamespace(cu_seqlens=i32(cu), slots=i32(slots), sequences=len(lengths),
                            token_seq=i32(np.repeat(np.arange(len(lengths)), lengths)),
-                           tokens=int(cu[-1]))
+                           tokens=int(cu[-1]), max_new=int(max(lengths)))
 
 
 # -- the norm on a sublayer's output --------------------------------------------------------
@@ -286,7 +286,10 @@ def test_selective_scan_over_pieces_with_a_token_far_back(dtype, channels, n_sta
             assert abs(y[-1, 0] - other[-1, 0]) > 0.05 * np.abs(y[-1]).max()
         seqs.append((x, low, z, dt, y * plain.silu(z)))
     state = torch.full((5, channels, n_state), 3.0, device=DEV)
-    for cuts in ((400, 5, 64), (1, 1, 1), (2, 2, 2), (63, 4, 33), (399, 1, 64)):
+    # (the second number: tokens a run when a step's part of a sequence is walked in runs)
+    for cuts, run in (((400, 5, 64), 0), ((1, 1, 1), 0), ((2, 2, 2), 0), ((63, 4, 33), 0),
+                      ((399, 1, 64), 0), ((400, 5, 64), 64), ((400, 5, 64), 16), ((130, 5, 33), 32),
+                      ((399, 1, 64), 7)):
         if cuts == (1, 1, 1) and n_state > 100:
             continue
         slots = [3, 0, 4]
@@ -302,19 +305,19 @@ def test_selective_scan_over_pieces_with_a_token_far_back(dtype, channels, n_sta
             dt = ops.step_size(low, rank, dev(w_dt, T), dev(b_dt, T))
             close(dt, cat(3), torch.float32, "step sizes")
             out = ops.selective_scan(dev(cat(0), T), dt, low, rank + 3, rank + 3 + n_state, n_state,
-                                     dev(cat(2)), dev(a_log, T), dev(d_skip, T), state, step)
+                                     dev(cat(2)), dev(a_log, T), dev(d_skip, T), state, step, run=run)
             for i, t, lo in zip(live, take, np.cumsum([0] + take)):
                 rows[i].append(out[lo:lo + t])
                 at[i] += t
         for i in range(3):
-            close(torch.cat(rows[i]), seqs[i][4], T, f"cuts {cuts}, sequence {i}")
+            close(torch.cat(rows[i]), seqs[i][4], T, f"cuts {cuts}, runs of {run}, sequence {i}")
     # a step that must leave the state as it was (a layer call that does not own its entry)
     before = state.clone()
     step = scan_step([5], [0])
     low = dev(seqs[1][1])
     ops.selective_scan(dev(seqs[1][0], T), ops.step_size(low, rank, dev(w_dt, T), dev(b_dt, T)),
                        low, rank + 3, rank + 3 + n_state, n_state, dev(seqs[1][2]), dev(a_log, T),
-                       dev(d_skip, T), state, step, keep_state=False)
+                       dev(d_skip, T), state, step, keep_state=False, run=2)
     assert torch.equal(state, before)
 
 
@@ -355,7 +358,9 @@ def test_fading_state_over_pieces_with_a_token_far_back(heads, dim, vdim, decay)
                      * out_scale))
     less_one = dev(np.asarray(decay, dtype=np.float64) - 1.0)
     state = torch.full((5, heads, vdim, dim), -2.0, device=DEV)
-    for cuts in ((400, 3, 70), (1, 1, 1), (2, 2, 2), (63, 3, 17), (399, 1, 70)):
+    for cuts, run in (((400, 3, 70), 0), ((1, 1, 1), 0), ((2, 2, 2), 0), ((63, 3, 17), 0),
+                      ((399, 1, 70), 0), ((400, 3, 70), 64), ((400, 3, 70), 16), ((130, 3, 33), 32),
+                      ((399, 1, 70), 7)):
         slots = [2, 4, 0]
         state[slots] = 0.0
         at = [0] * 3
@@ -366,7 +371,7 @@ def test_fading_state_over_pieces_with_a_token_far_back(heads, dim, vdim, decay)
             step = scan_step(take, [slots[i] for i in live])
             proj = dev(np.concatenate([seqs[i][0][at[i]:at[i] + t] for i, t in zip(live, take)]))
             y = ops.decay_attention(proj, 7, 7 + qk, 7 + 2 * qk, heads, dim, vdim, less_one, state,
-                                    step)
+                                    step, run=run)
             out = ops.norm_gate(y, dev(w, torch.bfloat16), proj[:, 7 + 2 * qk + vc:], eps,
                                 out_scale, torch.float32)
             for i, t, lo in zip(live, take, np.cumsum([0] + take)):
@@ -374,11 +379,12 @@ def test_fading_state_over_pieces_with_a_token_far_back(heads, dim, vdim, decay)
                 rows[i].append(out[lo:lo + t])
                 at[i] += t
         for i in range(3):
-            close(torch.cat(raw[i]), seqs[i][1], torch.float32, f"cuts {cuts}, sequence {i}")
+            close(torch.cat(raw[i]), seqs[i][1], torch.float32,
+                  f"cuts {cuts}, runs of {run}, sequence {i}")
             close(torch.cat(rows[i]), seqs[i][2], torch.float32, f"cuts {cuts}, normed {i}")
     before = state.clone()
     ops.decay_attention(dev(seqs[1][0]), 7, 7 + qk, 7 + 2 * qk, heads, dim, vdim, less_one, state,
-                        scan_step([3], [4]), keep_state=False)
+                        scan_step([3], [4]), keep_state=False, run=2)
     assert torch.equal(state, before)
     plain_out = ops.norm_gate(dev(seqs[1][1]), dev(w, torch.bfloat16), None, eps, 1.0, torch.bfloat16)
     close(plain_out, plain.rms_norm(seqs[1][1], w, eps), torch.bfloat16, "no gate")
