@@ -346,6 +346,22 @@ def kernel_case(name: str) -> int:
         qkv = torch.randn(n, (A + 2 * G) * d, device=dev, dtype=torch.bfloat16)
         run = lambda i: ops.attention_prefill_tc(qkv, k, v, *plan, lens, table, A, G, d, d ** -0.5,
                                                  None)
+    elif name == "selective_scan_4096":
+        # the selective scan over one prompt of 4,096 tokens at the `2k` size of `--design
+        # zodirax` (4,096 channels of 16 states), walked in runs of 64 tokens: about 220 MB
+        from types import SimpleNamespace
+        n, ch, ns, rank = 4096, 4096, 16, 128
+        x = torch.randn(n, ch, device=dev, dtype=torch.bfloat16)
+        low = torch.randn(n, rank + 2 * ns, device=dev)
+        dt = torch.rand(n, ch, device=dev) * 0.1
+        z = torch.randn(n, ch, device=dev)
+        a_log = torch.rand(ch, ns, device=dev, dtype=torch.bfloat16)
+        skip = torch.ones(ch, device=dev, dtype=torch.bfloat16)
+        state = torch.zeros(1, ch, ns, device=dev)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        step = SimpleNamespace(cu_seqlens=i32([0, n]), slots=i32([0]), sequences=1, max_new=n)
+        run = lambda i: ops.selective_scan(x, dt, low, rank, rank + ns, ns, z, a_log, skip, state,
+                                           step, run=64)
     else:
         raise SystemExit(f"unknown kernel case {name}")
     for i in range(4):
@@ -796,7 +812,7 @@ def main() -> int:
     ap.add_argument("--design-sizes", default="1k,2k", help="which of: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--kernel", default=None,
                     help="run one kernel case for a profiler: gemm_gateup_b8, gemm_down_b8, "
-                         "gemm_head_b8, gemm_gated_2048, attention_decode_b64, "
+                         "gemm_head_b8, gemm_gated_2048, selective_scan_4096, attention_decode_b64, "
                          "attention_prefill_2048")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
