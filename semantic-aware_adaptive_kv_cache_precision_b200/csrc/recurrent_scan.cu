@@ -87,6 +87,32 @@ __global__ void conv_state_kernel(const float* __restrict__ in, long long stride
   }
 }
 
+// Both of the above in one launch for a step in which every sequence brings one token: a
+// thread a (sequence, channel) reads the running inputs, adds the products in the same order
+// as the kernel above, and moves the running inputs up by one.
+template <typename W, typename C>
+__global__ void conv_step_kernel(const float* __restrict__ in, long long stride,
+                                 const W* __restrict__ w, const W* __restrict__ bias,
+                                 float* __restrict__ state, const int32_t* __restrict__ slots,
+                                 C* __restrict__ out, int channels, int taps, long long count,
+                                 int keep_state) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= count) return;
+  const long long b = idx / channels;
+  const int c = static_cast<int>(idx - b * channels);
+  float* old = state + (long long)slots[b] * (taps - 1) * channels + c;
+  const float now = in[b * stride + c];
+  float acc = bias ? widen(bias[c]) : 0.f;
+  for (int j = 0; j + 1 < taps; ++j)
+    acc = fmaf(old[(long long)j * channels], widen(w[(long long)c * taps + j]), acc);
+  acc = fmaf(now, widen(w[(long long)c * taps + taps - 1]), acc);
+  out[idx] = narrow<C>(silu(acc));
+  if (keep_state && taps > 1) {
+    for (int j = 0; j + 2 < taps; ++j) old[(long long)j * channels] = old[(long long)(j + 1) * channels];
+    old[(long long)(taps - 2) * channels] = now;
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Step sizes: dt[t, c] = softplus(sum_r low[t, r] Wdt[c, r] + b[c]), a tiled fp32 product
 // (plain FFMA): a block of 256 threads makes BM tokens x 64 channels, a thread TM x 4 of
@@ -173,7 +199,8 @@ __global__ void selective_scan_kernel(const C* __restrict__ x, const float* __re
                                       const int32_t* __restrict__ slots, C* __restrict__ out,
                                       int channels, int n_state, int lanes, int keep_state,
                                       int chunk_len, int max_chunks, float* __restrict__ scratch,
-                                      float* __restrict__ dt_sums) {
+                                      float* __restrict__ dt_sums, const W* __restrict__ w_dt,
+                                      const W* __restrict__ b_dt, int rank) {
   const int b = PHASE == 0 ? blockIdx.y : blockIdx.y / max_chunks;
   const int run = PHASE == 0 ? 0 : blockIdx.y % max_chunks;
   int first = cu_seqlens[b], last = cu_seqlens[b + 1];
@@ -200,7 +227,18 @@ __global__ void selective_scan_kernel(const C* __restrict__ x, const float* __re
   const float skip = widen(d_skip[c]);
   float dt_sum = 0.f;
   for (int t = first; t < last; ++t) {
-    const float step = dt[(long long)t * channels + c];
+    float step;
+    if (PHASE == 0 && dt == nullptr) {
+      // the step size made here (a step of few tokens): the same products in the same order
+      // as the tiled kernel adds them
+      const float* lt = low + (long long)t * low_stride;
+      const W* wr = w_dt + (long long)c * rank;
+      float acc = 0.f;
+      for (int r = 0; r < rank; ++r) acc = fmaf(lt[r], widen(wr[r]), acc);
+      step = softplus(acc + (b_dt ? widen(b_dt[c]) : 0.f));
+    } else {
+      step = dt[(long long)t * channels + c];
+    }
     const float xv = widen(x[(long long)t * channels + c]);
     const float* bt = low + (long long)t * low_stride + b_off + n0;
     const float* ct = low + (long long)t * low_stride + c_off + n0;
@@ -437,6 +475,27 @@ SAKV_EXPORT int sakv_conv_state(const float* in, long long stride, float* state,
                         stream, in, stride, state, cu_seqlens, slots, channels, taps, sequences);
 }
 
+// `sakv_causal_conv` and `sakv_conv_state` in one launch for a step in which each of `sequences`
+// sequences brings one token (token b belongs to sequence b).
+SAKV_EXPORT int sakv_conv_step(const float* in, long long stride, const void* w, const void* bias,
+                               int w_dtype, float* state, const int32_t* slots, void* out,
+                               int out_dtype, int sequences, int channels, int taps,
+                               int keep_state, cudaStream_t stream) {
+  if (sequences < 0 || channels <= 0 || taps < 1 || taps > 64) return cudaErrorInvalidValue;
+  if (sequences == 0) return 0;
+  const long long count = (long long)sequences * channels;
+  const dim3 grid((unsigned)((count + 127) / 128)), block(128);
+#define SAKV_CONV(W, C)                                                                          \
+  return launch_ordered(conv_step_kernel<W, C>, grid, block, 0, stream, in, stride, (const W*)w, \
+                        (const W*)bias, state, slots, (C*)out, channels, taps, count, keep_state)
+  if (w_dtype == SAKV_F32 && out_dtype == SAKV_F32) SAKV_CONV(float, float);
+  if (w_dtype == SAKV_BF16 && out_dtype == SAKV_BF16) SAKV_CONV(__nv_bfloat16, __nv_bfloat16);
+  if (w_dtype == SAKV_BF16 && out_dtype == SAKV_F32) SAKV_CONV(__nv_bfloat16, float);
+  if (w_dtype == SAKV_F32 && out_dtype == SAKV_BF16) SAKV_CONV(float, __nv_bfloat16);
+#undef SAKV_CONV
+  return cudaErrorInvalidValue;
+}
+
 // low: fp32 [tokens, stride], its first `rank` columns; w: [channels, rank], bias [channels]
 // of `w_dtype`; dt: fp32 [tokens, channels].
 SAKV_EXPORT int sakv_step_size(const float* low, long long stride, int rank, const void* w,
@@ -466,7 +525,8 @@ SAKV_EXPORT int sakv_step_size(const float* low, long long stride, int rank, con
 // low: fp32 [tokens, low_stride] with B at column b_off and C at c_off (n_state each); z: fp32
 // rows `z_stride` apart (the gate's pre-activation); a_log [channels, n_state], d_skip
 // [channels] of `w_dtype`; state: fp32 [slots, channels, n_state]. out: [tokens, channels] of
-// `c_dtype` = (scan + d_skip x) * silu(z).
+// `c_dtype` = (scan + d_skip x) * silu(z). `dt` null: dt = softplus(low[:, :rank] w_dt^T + b_dt)
+// is made in the kernel (w_dt [channels, rank], b_dt [channels] or null, of `w_dtype`).
 SAKV_EXPORT int sakv_selective_scan(const void* x, int c_dtype, const float* dt, const float* low,
                                     long long low_stride, int b_off, int c_off, const float* z,
                                     long long z_stride, const void* a_log, const void* d_skip,
@@ -474,9 +534,12 @@ SAKV_EXPORT int sakv_selective_scan(const void* x, int c_dtype, const float* dt,
                                     const int32_t* slots, void* out, int tokens, int sequences,
                                     int channels, int n_state, int keep_state, int chunk_len,
                                     int max_chunks, float* scratch, float* dt_sums,
+                                    const void* w_dt, const void* b_dt, int rank,
                                     cudaStream_t stream) {
   if (tokens < 0 || sequences < 0 || channels <= 0 || n_state <= 0 || n_state > 512)
     return cudaErrorInvalidValue;
+  // dt null: the step sizes are made in the kernel from low's first `rank` columns (one walk only)
+  if (dt == nullptr && (w_dt == nullptr || rank <= 0 || chunk_len > 0)) return cudaErrorInvalidValue;
   if (tokens == 0 || sequences == 0) return 0;
   const bool runs = chunk_len > 0;
   if (runs && (max_chunks <= 0 || scratch == nullptr || dt_sums == nullptr ||
@@ -494,7 +557,8 @@ SAKV_EXPORT int sakv_selective_scan(const void* x, int c_dtype, const float* dt,
   launch_ordered(selective_scan_kernel<NPT, PHASE, W, C>, grid, dim3(block), 0, stream,          \
                  (const C*)x, dt, low, low_stride, b_off, c_off, z, z_stride, (const W*)a_log,   \
                  (const W*)d_skip, state, cu_seqlens, slots, (C*)out, channels, n_state, lanes,  \
-                 keep_state, chunk_len, max_chunks, scratch, dt_sums)
+                 keep_state, chunk_len, max_chunks, scratch, dt_sums, (const W*)w_dt,            \
+                 (const W*)b_dt, rank)
 #define SAKV_SCAN_ALL(NPT, W, C)                                                                 \
   do {                                                                                           \
     if (!runs) return SAKV_SCAN(NPT, 0, W, C);                                                   \

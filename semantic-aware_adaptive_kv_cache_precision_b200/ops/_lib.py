@@ -45,7 +45,8 @@ SIGNATURES = {
     "sakv_conv_state": ("recurrent_scan", [P, L, P, P, P, I, I, I, P]),
     "sakv_step_size": ("recurrent_scan", [P, L, I, P, P, I, P, I, I, P]),
     "sakv_selective_scan": ("recurrent_scan", [P, I, P, P, L, I, I, P, L, P, P, I, P, P, P, P,
-                                               I, I, I, I, I, I, I, P, P, P]),
+                                               I, I, I, I, I, I, I, P, P, P, P, I, P]),
+    "sakv_conv_step": ("recurrent_scan", [P, L, P, P, I, P, P, P, I, I, I, I, I, P]),
     "sakv_decay_attention": ("recurrent_scan", [P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, I,
                                                 I, I, P, P]),
     "sakv_norm_gate": ("recurrent_scan", [P, P, I, P, L, P, I, I, I, F, F, P]),

@@ -32,6 +32,12 @@ def causal_conv(xz: torch.Tensor, channels: int, weight: torch.Tensor,
            and tuple(state.shape[1:]) == (taps - 1, channels),
            "state: fp32 [slots, taps - 1, channels]")
     out = torch.empty((tokens, channels), dtype=out_dtype, device=xz.device)
+    if getattr(step, "is_decode", False) and tokens == step.sequences:
+        # every sequence brings one token: output and running inputs in one launch
+        call("sakv_conv_step", ptr(xz), xz.stride(0), ptr(weight), ptr(bias),
+             dtype_code(weight.dtype), ptr(state), ptr(step.slots), ptr(out),
+             dtype_code(out_dtype), tokens, channels, taps, int(keep_state))
+        return out
     call("sakv_causal_conv", ptr(xz), xz.stride(0), ptr(weight), ptr(bias),
          dtype_code(weight.dtype), ptr(state), ptr(step.cu_seqlens), ptr(step.token_seq),
          ptr(step.slots), ptr(out), dtype_code(out_dtype), tokens, channels, taps)
@@ -57,10 +63,11 @@ def step_size(low: torch.Tensor, rank: int, weight: torch.Tensor,
     return dt
 
 
-def selective_scan(x: torch.Tensor, dt: torch.Tensor, low: torch.Tensor, b_off: int, c_off: int,
-                   n_state: int, z: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
-                   state: torch.Tensor, step, keep_state: bool = True,
-                   run: int = 0) -> torch.Tensor:
+def selective_scan(x: torch.Tensor, dt: torch.Tensor | None, low: torch.Tensor, b_off: int,
+                   c_off: int, n_state: int, z: torch.Tensor, a_log: torch.Tensor,
+                   d_skip: torch.Tensor, state: torch.Tensor, step, keep_state: bool = True,
+                   run: int = 0, dt_weight: torch.Tensor | None = None,
+                   dt_bias: torch.Tensor | None = None) -> torch.Tensor:
     """`S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n; y_c = sum_n S[c, n] C_n + D_c x_c`
     over each sequence's tokens, A = -exp(a_log); returns `y * silu(z)` [T, channels] of x's
     type. `x`: [T, channels]; `dt`: fp32 [T, channels]; B and C: `n_state` columns of fp32
@@ -70,11 +77,26 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, low: torch.Tensor, b_off: 
     `run` 0: one walk over each sequence's tokens, so the sums do not depend on how a sequence
     was cut into steps. `run` r > 0: a sequence's tokens are walked in runs of r side by side
     (three launches: the runs from zero, the states carried from run to run, the runs again
-    with their outputs); `step.max_new` bounds a sequence's tokens."""
-    require_cuda(x, dt, low, z, a_log, d_skip, state)
+    with their outputs); `step.max_new` bounds a sequence's tokens.
+
+    `dt` None (a step of few tokens, one walk): the kernel makes the step sizes itself,
+    `softplus(low[:, :rank] dt_weight^T + dt_bias)` with `dt_weight` [channels, rank] of
+    a_log's type, adding the products in the order `step_size` adds them."""
+    require_cuda(x, dt, low, z, a_log, d_skip, state, dt_weight, dt_bias)
     tokens, channels = x.shape
-    _check(x.is_contiguous() and dt.dtype == torch.float32 and dt.is_contiguous()
-           and dt.shape == x.shape, "x: [T, channels]; dt: fp32 of the same shape")
+    rank = 0
+    if dt is None:
+        _check(not run and dt_weight is not None and dt_weight.dim() == 2
+               and dt_weight.shape[0] == channels and dt_weight.is_contiguous()
+               and dt_weight.dtype == a_log.dtype and dt_weight.shape[1] <= low.shape[1]
+               and (dt_bias is None or (dt_bias.shape == (channels,) and dt_bias.is_contiguous()
+                                        and dt_bias.dtype == a_log.dtype)),
+               "without dt: dt_weight [channels, rank] (and dt_bias [channels]) of a_log's type, "
+               "one walk")
+        rank = dt_weight.shape[1]
+    _check(x.is_contiguous() and (dt is None or (dt.dtype == torch.float32 and dt.is_contiguous()
+                                                 and dt.shape == x.shape)),
+           "x: [T, channels]; dt: fp32 of the same shape")
     _check(low.dtype == torch.float32 and low.dim() == 2 and low.stride(1) == 1
            and max(b_off, c_off) + n_state <= low.shape[1] and low.shape[0] == tokens,
            "low: fp32 [T, columns] holding B and C")
@@ -91,7 +113,7 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, low: torch.Tensor, b_off: 
          int(b_off), int(c_off), ptr(z), z.stride(0), ptr(a_log), ptr(d_skip),
          dtype_code(a_log.dtype), ptr(state), ptr(step.cu_seqlens), ptr(step.slots), ptr(out),
          tokens, step.sequences, channels, n_state, int(keep_state), int(run) if runs else 0,
-         runs, ptr(scratch), ptr(sums))
+         runs, ptr(scratch), ptr(sums), ptr(dt_weight), ptr(dt_bias), int(rank))
     return out
 
 

@@ -74,10 +74,12 @@ class SelectiveScanMixer(Part):
         x = ops.causal_conv(xz, s.inner, self.conv_w, self.conv_b, conv_view.state, step,
                             self.act_dtype, keep_state=write_cache)
         low = ops.linear(x, self.w_x, out_dtype=torch.float32)
-        dt = ops.step_size(low, s.dt_rank, self.w_dt, self.b_dt)
+        # a step of one token a sequence makes its step sizes inside the scan's kernel
+        dt = None if step.is_decode else ops.step_size(low, s.dt_rank, self.w_dt, self.b_dt)
         y = ops.selective_scan(x, dt, low, s.dt_rank, s.dt_rank + s.state, s.state,
                                xz[:, s.inner:], self.a_log, self.d_skip, scan_view.state, step,
-                               keep_state=write_cache, run=self._run(step))
+                               keep_state=write_cache, run=self._run(step),
+                               dt_weight=self.w_dt, dt_bias=self.b_dt)
         return ops.linear(y, self.w_o, out_dtype=torch.float32)
 
     def forward(self, h, step, view, residual, write_cache=True):

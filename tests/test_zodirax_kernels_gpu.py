@@ -23,7 +23,8 @@ def scan_step(lengths, slots):
     cu = np.concatenate([[0], np.cumsum(lengths)])
     return SimpleNamespace(cu_seqlens=i32(cu), slots=i32(slots), sequences=len(lengths),
                            token_seq=i32(np.repeat(np.arange(len(lengths)), lengths)),
-                           tokens=int(cu[-1]), max_new=int(max(lengths)))
+                           tokens=int(cu[-1]), max_new=int(max(lengths)),
+                           is_decode=all(n == 1 for n in lengths))
 
 
 # -- the norm on a sublayer's output --------------------------------------------------------
@@ -304,8 +305,12 @@ def test_selective_scan_over_pieces_with_a_token_far_back(dtype, channels, n_sta
             low = dev(cat(1))
             dt = ops.step_size(low, rank, dev(w_dt, T), dev(b_dt, T))
             close(dt, cat(3), torch.float32, "step sizes")
+            if step.is_decode:                      # the kernel makes the step sizes itself
+                dt = None
             out = ops.selective_scan(dev(cat(0), T), dt, low, rank + 3, rank + 3 + n_state, n_state,
-                                     dev(cat(2)), dev(a_log, T), dev(d_skip, T), state, step, run=run)
+                                     dev(cat(2)), dev(a_log, T), dev(d_skip, T), state, step,
+                                     run=0 if dt is None else run,
+                                     dt_weight=dev(w_dt, T), dt_bias=dev(b_dt, T))
             for i, t, lo in zip(live, take, np.cumsum([0] + take)):
                 rows[i].append(out[lo:lo + t])
                 at[i] += t
