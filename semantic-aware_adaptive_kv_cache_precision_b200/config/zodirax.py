@@ -115,8 +115,9 @@ class ZodiraxConfig:
                     problems.append(f"{mw}state up to 512 and conv up to 64 are what the scan "
                                     "kernels take")
             elif kind == "parallel":
-                mixer = {"left_scale": number(mw, m, "left_scale"),
-                         "right_scale": number(mw, m, "right_scale")}
+                # (a scale that config.json does not give is not applied)
+                mixer = {k: 1.0 if m.get(k) is None else number(mw, m, k)
+                         for k in ("left_scale", "right_scale")}
                 left, lw = m.get("left"), mw + "left."
                 if not isinstance(left, dict):
                     problems.append(f"{lw[:-1]}: expected an object with the attention's sizes")
@@ -131,7 +132,7 @@ class ZodiraxConfig:
                 if a["dim"] > 640 or a["vdim"] > 512:
                     problems.append(f"{lw}dim up to 640 and vdim up to 512 are what the attention "
                                     "kernel takes")
-                a["scale"] = number(lw, left, "scale")
+                a["scale"] = 1.0 if left.get("scale") is None else number(lw, left, "scale")
                 mask = left.get("mask")
                 if mask is None:
                     a["mask"] = None

@@ -141,7 +141,8 @@ def window_attention(h, t, p, m, eps):
     out = np.empty((n, H, Dv))
     for head in range(H):
         g = head // (H // G)
-        w = sink_softmax(q[:, head] @ k[:, g].T * m["scale"], mask, float(t[p + "sink"][head]))
+        w = sink_softmax(q[:, head] @ k[:, g].T * m.get("scale", 1.0), mask,
+                         float(t[p + "sink"][head]))
         out[:, head] = w @ v[:, g]
     return out.reshape(n, H * Dv) @ t[p + "o"].T
 
@@ -164,8 +165,9 @@ def decayed_linear_attention(h, t, p, m, eps):
 
 
 def parallel_mixer(h, t, p, m, eps):
-    return (m["left_scale"] * window_attention(h, t, p + "left.", m["left"], eps)
-            + m["right_scale"] * decayed_linear_attention(h, t, p + "right.", m["right"], eps))
+    return (m.get("left_scale", 1.0) * window_attention(h, t, p + "left.", m["left"], eps)
+            + m.get("right_scale", 1.0) * decayed_linear_attention(h, t, p + "right.", m["right"],
+                                                                   eps))
 
 
 def gated_mlp(h, t, p):

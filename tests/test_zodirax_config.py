@@ -149,3 +149,18 @@ def test_the_scan_and_the_fading_state_by_hand():
 def test_sizes_differ_between_the_configurations():
     widths = {c["width"] for c, _ in CONFIGS.values()}
     assert len(widths) == len(CONFIGS) and WIDE["layers"][1]["mixer"]["state"] > 128
+
+
+def test_what_config_json_does_not_give_is_not_applied():
+    bare = copy.deepcopy(MIXED)
+    mixer = bare["layers"][0]["mixer"]
+    for key in ("left_scale", "right_scale"):
+        del mixer[key]
+    for key in ("scale", "kv_heads", "vdim"):
+        del mixer["left"][key]
+    del mixer["left"]["rot"]["scaling"], mixer["left"]["mask"]["keep_first"], bare["embedding"]
+    spec = config_from_dict(bare).model_spec()
+    left, right = spec.blocks[0].mixer.left, spec.blocks[0].mixer.right
+    assert (left.out_scale, right.out_scale, left.scale, spec.embed_scale) == (1.0, 1.0, 1.0, 1.0)
+    assert (left.kv_heads, left.value_dim, left.keep_first) == (left.heads, left.head_dim, 0)
+    assert left.position.scaling is None

@@ -38,7 +38,7 @@ def draw(seed):
             heads = pick([1, 2, 3, 5, 6])
             left = (kv_heads * pick([1, 2, 3]), kv_heads, dim, pick([8, 12, 32, 80, 96]),
                     float(dim ** -0.5 * rng.uniform(0.5, 2)), pick([1, 2, 7, 31, 64, 65, 96, 130, 500]),
-                    pick([0, 0, 1, 4, 9, 64, 66]), rot(float(pick([100, 1e4, 2e4, 5e5])), dims, scaling))
+                    pick([0, 0, 1, 4, 9, 64, 66]), rot(float(pick([100, 1e4, 3e4, 5e5])), dims, scaling))
             right = (heads, pick([8, 12, 32, 40, 64]), pick([8, 20, 32, 48]),
                      [float(pick([1.0, 0.999, 0.99, 0.9, 0.6, 0.2])) for _ in range(heads)])
             layers.append(pair(left, right, (float(rng.uniform(0.3, 2)), float(rng.uniform(0.3, 2))),
