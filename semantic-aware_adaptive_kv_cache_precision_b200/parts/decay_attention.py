@@ -7,7 +7,9 @@
 
 The fused projection leaves fp32 (its accumulator, unrounded); the silus, the recurrence, the
 norm and the gate are fp32 in both modes (`csrc/recurrent_scan.cu`). The state lives in the
-cache as fixed-size per-sequence state, stored as its transpose [heads, value_dim, dim].
+cache as fixed-size per-sequence state, stored as its transpose [heads, value_dim, dim]. The
+state moves by its change, `S += (decay - 1) S + k v^T`, with `decay - 1` rounded once from the
+exact number; in bfloat16 a long part of a prompt is walked in runs of `RUN` tokens side by side.
 
 The part is a mixer of its own (`produce`) and a branch of a `ParallelMixer`.
 """

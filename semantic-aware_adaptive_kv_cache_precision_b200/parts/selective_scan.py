@@ -10,6 +10,10 @@ Both projections that feed the recurrence leave fp32 (their accumulators, unroun
 sizes (a product in fp32 and softplus), the decays and their exponentials, the state, the sums
 over it and the gate are fp32 in both modes (`csrc/recurrent_scan.cu`). A sequence's state (S,
 and the convolution's last `taps - 1` inputs) lives in the cache as two fixed-size states.
+
+In bfloat16 a long part of a prompt is walked in runs of `RUN` tokens side by side. A step of
+one token a sequence runs the convolution with its state update in one launch, and the scan's
+kernel makes the step sizes itself.
 """
 
 from __future__ import annotations
