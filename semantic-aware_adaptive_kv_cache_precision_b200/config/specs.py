@@ -65,8 +65,10 @@ class BandScaling:
 
 @dataclass(frozen=True)
 class RotarySpec:
-    """Rotate-half rotary position encoding of the first `rotary_dim` of each head;
-    `scaling` (a `RampScaling` or a `BandScaling`) stretches its long wavelengths."""
+    """Rotary position encoding of the first `rotary_dim` of each head; `scaling` (a
+    `RampScaling` or a `BandScaling`) stretches its long wavelengths. `kind` "rotary_half"
+    pairs dimension i with i + rotary_dim / 2, "rotary_interleaved" pairs 2i with 2i + 1; the
+    pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a), a = p f_i."""
     head_dim: int
     rotary_dim: int
     theta: float
@@ -166,10 +168,13 @@ class LatentAttentionSpec:
     is [Wuk_h c | rotated part], its value Wuv_h c; its query [`head_dim` plain | `rot_dim`
     rotated] comes from a query latent of `q_rank` numbers (normed like c; None: straight
     from the input). The cache holds c and the rotated part only. `position.rotary_dim`
-    must be `rot_dim`.
+    must be `rot_dim`. `window` w: query i sees key j only if 0 <= i - j < w (None: every
+    earlier key). `sink`: the softmax's denominator of head h also holds `exp(sink[h])`, a
+    learned number that has no key and no value. `head_gate`: head h's output is multiplied
+    by `sigmoid(Wg x)[h]`, one number a head, read from the mixer's input.
 
     Tensor names after the part's prefix: `dq`, `dq.norm`, `uq` (or `q` without a query
-    latent), `dkv`, `dkv.norm`, `uk`, `uv`, `o`."""
+    latent), `dkv`, `dkv.norm`, `uk`, `uv`, `o`, `sink`, `g`."""
     hidden: int
     heads: int
     head_dim: int
@@ -180,6 +185,9 @@ class LatentAttentionSpec:
     scale: float
     eps: float
     position: RotarySpec
+    window: Optional[int] = None
+    sink: bool = False
+    head_gate: bool = False
     kind: str = "latent_attention"
 
 
@@ -223,14 +231,18 @@ class ClampedExpertSpec:
 class RoutedExpertsSpec:
     """A mixture of `experts` small feed-forwards (`e0`, `e1`, ...; all of form `expert`) of
     which each token uses the `top` with the largest router scores. `score` "sigmoid":
-    each expert's score is the sigmoid of its router logit (fp32). `renormalize`: whether
-    the chosen scores are divided by their sum. `weight_input`: the score multiplies the
-    expert's input (out = sum expert(w x)) rather than its output. `shared`: one more
-    expert that every token uses, multiplied by `sigmoid(Wsg x)`, one number a token
-    (`shared.sg`), if `shared_gate`.
+    each expert's score is the sigmoid of its router logit (fp32); "softmax": the softmax of
+    the logits over all the router's outputs. `correction`: a learned number an output
+    (`correction`) is added to the scores for the CHOICE only; the weights are the scores
+    without it. `identity` n: the router has n more outputs after the experts'; an "expert"
+    chosen among them has no tensors and returns its input (times the weight).
+    `renormalize`: whether the chosen scores are divided by their sum. `weight_input`: the
+    score multiplies the expert's input (out = sum expert(w x)) rather than its output.
+    `shared`: one more expert that every token uses, multiplied by `sigmoid(Wsg x)`, one
+    number a token (`shared.sg`), if `shared_gate`.
 
-    Tensor names after the part's prefix: `router`, `e<i>.gate`, `e<i>.up`, `e<i>.down`,
-    `shared.gate`, `shared.up`, `shared.down`, `shared.sg`."""
+    Tensor names after the part's prefix: `router`, `correction`, `e<i>.gate`, `e<i>.up`,
+    `e<i>.down`, `shared.gate`, `shared.up`, `shared.down`, `shared.sg`."""
     hidden: int
     experts: int
     top: int
@@ -240,6 +252,8 @@ class RoutedExpertsSpec:
     score: str = "sigmoid"
     renormalize: bool = False
     weight_input: bool = True
+    correction: bool = False
+    identity: int = 0
     kind: str = "routed_experts"
 
 
@@ -288,6 +302,12 @@ class DecayAttentionSpec:
     multiplied by a weight, by `sigmoid(Wg x)` element by element (`gate`) and by `out_scale`,
     and projected.
 
+    The variations, each a field: `activation` None leaves q, k, v as projected; `position`
+    turns the first `rotary_dim` numbers of every head of q and k by the token's position;
+    `key_scale` multiplies k (after the rotation); `norm` "head" divides each head's output by
+    its own root mean square instead of all heads' together; `norm_weight` False: the norm has
+    no weight; `gate_kind` "silu": the gate is `silu(Wg x)`.
+
     Tensor names after the part's prefix: `q`, `k`, `v`, `g`, `norm`, `o`."""
     hidden: int
     heads: int
@@ -297,6 +317,12 @@ class DecayAttentionSpec:
     eps: float
     gate: bool = True
     out_scale: float = 1.0
+    activation: Optional[str] = "silu"
+    position: Optional[RotarySpec] = None
+    key_scale: float = 1.0
+    norm: str = "all"
+    norm_weight: bool = True
+    gate_kind: str = "sigmoid"
     kind: str = "decay_attention"
 
 
@@ -350,13 +376,14 @@ class BlockSpec:
     """One layer: how a mixer and a feed-forward are arranged around the residual.
 
     `prefix` is where the block's tensors sit in the checkpoint
-    ("model.layers.3."); the parts append their own names to it.
+    ("model.layers.3."); the parts append their own names to it. `ffn` None: the layer has
+    no feed-forward (and no norm before it).
     """
     prefix: str
     mixer: object
     mixer_norm: NormSpec
     ffn: object
-    ffn_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
     mixer_name: str = "self_attn"
     ffn_name: str = "mlp"
     mixer_norm_name: str = "input_layernorm"

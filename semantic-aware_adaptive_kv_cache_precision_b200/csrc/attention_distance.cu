@@ -60,6 +60,11 @@ struct AttentionExtra {
   // head) the softmax's denominator also holds exp(sink[h]): a logit without key or value.
   int keep;
   const float* sink;
+  // A gate a head from a tensor of its own (queries that are not part of the projection the
+  // gates came with): head h's output is multiplied by sigmoid(head_gate[t * stride + h]),
+  // elements of the queries' type. Null: none (or `gate_off` inside qkv).
+  const void* head_gate;
+  long long head_gate_stride;
 };
 
 namespace {
@@ -645,6 +650,10 @@ distance_attention_tiled_kernel(
     if (gate_off >= 0) {
       const float z = widen(qkv[(long long)t * stride + gate_off + h0 + p]);
       gate = 1.f / (1.f + expf(-z));
+    } else if (x.head_gate != nullptr) {
+      const float z = widen(static_cast<const T*>(x.head_gate)[(long long)t * x.head_gate_stride +
+                                                                h0 + p]);
+      gate = 1.f / (1.f + expf(-z));
     }
     const float inv = gate * x.out_scale / l[p];
 #pragma unroll
@@ -868,8 +877,10 @@ SAKV_EXPORT int sakv_cached_attention(
     int max_blocks, int tokens, int heads, int kv_heads, int maps, int dim, int vdim, float scale,
     int window, int chunk, float lambda, float out_scale, float eps, int gate_elem_off,
     int splits, int key_splits, float* scratch, long long scratch_floats, int* tickets,
-    int warp_stage, int heads_first, int keep_first, const float* sink, cudaStream_t stream) {
+    int warp_stage, int heads_first, int keep_first, const float* sink, const void* head_gate,
+    long long head_gate_stride, cudaStream_t stream) {
   if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return cudaErrorInvalidValue;
+  if (head_gate != nullptr && (maps != 1 || gate_off >= 0)) return cudaErrorInvalidValue;
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
       dim > 640 || vdim > 512 || max_blocks <= 0 || window < 0 || chunk < 0 ||
       (window > 0 && chunk > 0) || splits < 1 || splits > 16 || (maps != 1 && maps != 2) ||
@@ -901,6 +912,8 @@ SAKV_EXPORT int sakv_cached_attention(
   x.heads_first = heads_first && splits == 1;
   x.keep = window > 0 ? keep_first : 0;
   x.sink = sink;
+  x.head_gate = head_gate;
+  x.head_gate_stride = head_gate_stride;
   const void* values = x.v_in_k ? k_cache : v_cache;
   if (dtype == SAKV_F32)
     return pick_tiled<float>(qkv, stride, gate_off, out, k_cache, values, positions, token_seq,

@@ -5,10 +5,11 @@
 //   * divides the query latent by its root mean square (eps inside the root), multiplies by
 //     its weight and stores it for the up projection,
 //   * does the same to the key/value latent and writes it to the token's cache row,
-//   * rotates the shared key part by the token's position (pairs (i, i + rot/2), table of
-//     cosines and sines that already carry the rotation's magnitude) and writes it behind
-//     the latent in the same cache row.
-// `rotate_heads`: rotates a slice of every head of a projection's output in place.
+//   * rotates the shared key part by the token's position (pairs (i, i + rot/2), or with
+//     `interleaved` (2i, 2i + 1); table of cosines and sines that already carry the
+//     rotation's magnitude) and writes it behind the latent in the same cache row.
+// `rotate_heads`: rotates a slice of every head of a projection's output in place, with
+// the same two ways of pairing.
 // Sums of squares, norms and rotations are fp32 in both modes.
 #include "common.cuh"
 
@@ -24,7 +25,8 @@ latent_prepare_kernel(const float* __restrict__ down, long long stride, int q_ra
                       const int32_t* __restrict__ token_seq,
                       const int32_t* __restrict__ block_table, int max_blocks,
                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                      T* __restrict__ q_latent, T* __restrict__ cache, int write_cache) {
+                      T* __restrict__ q_latent, T* __restrict__ cache, int write_cache,
+                      int interleaved) {
   __shared__ float scratch[33];
   const long long t = blockIdx.x;
   const float* row = down + t * stride;
@@ -49,9 +51,10 @@ latent_prepare_kernel(const float* __restrict__ down, long long stride, int q_ra
   const float* part = kv + rank;
   for (int i = threadIdx.x; i < half; i += kThreads) {
     const float c = cos_t[(long long)pos * half + i], sn = sin_t[(long long)pos * half + i];
-    const float u = part[i], v = part[i + half];
-    to[rank + i] = narrow<T>(u * c - v * sn);
-    to[rank + half + i] = narrow<T>(v * c + u * sn);
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+    const float u = part[a], v = part[b];
+    to[rank + a] = narrow<T>(u * c - v * sn);
+    to[rank + b] = narrow<T>(v * c + u * sn);
   }
 }
 
@@ -60,7 +63,8 @@ __global__ void rotate_heads_kernel(T* __restrict__ x, long long stride, int hea
                                     int offset, int heads, int rot,
                                     const int32_t* __restrict__ positions,
                                     const float* __restrict__ cos_t,
-                                    const float* __restrict__ sin_t, long long count) {
+                                    const float* __restrict__ sin_t, long long count,
+                                    int interleaved) {
   const int half = rot / 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
        i += (long long)gridDim.x * blockDim.x) {
@@ -70,10 +74,11 @@ __global__ void rotate_heads_kernel(T* __restrict__ x, long long stride, int hea
     const long long t = rest / heads;
     const int pos = positions[t];
     const float c = cos_t[(long long)pos * half + e], sn = sin_t[(long long)pos * half + e];
-    T* p = x + t * stride + (long long)h * head_stride + offset + e;
-    const float u = widen(p[0]), v = widen(p[half]);
+    T* p = x + t * stride + (long long)h * head_stride + offset + (interleaved ? 2 * e : e);
+    const int other = interleaved ? 1 : half;
+    const float u = widen(p[0]), v = widen(p[other]);
     p[0] = narrow<T>(u * c - v * sn);
-    p[half] = narrow<T>(v * c + u * sn);
+    p[other] = narrow<T>(v * c + u * sn);
   }
 }
 
@@ -82,25 +87,26 @@ int prepare(const float* down, long long stride, int q_rank, int rank, int rot,
             const void* q_weight, const void* kv_weight, float eps, const int32_t* positions,
             const int32_t* token_seq, const int32_t* block_table, int max_blocks,
             const float* cos_t, const float* sin_t, void* q_latent, void* cache, int write_cache,
-            int tokens, cudaStream_t stream) {
+            int interleaved, int tokens, cudaStream_t stream) {
   return launch_ordered(latent_prepare_kernel<W, T>, dim3(tokens), dim3(kThreads), 0, stream, down,
                         stride, q_rank, rank, rot, (const W*)q_weight, (const W*)kv_weight, eps,
                         positions, token_seq, block_table, max_blocks, cos_t, sin_t,
-                        (T*)q_latent, (T*)cache, write_cache);
+                        (T*)q_latent, (T*)cache, write_cache, interleaved);
 }
 
 }  // namespace
 
 // down: fp32 [tokens, stride], columns [q_rank | rank | rot]. q_latent: [tokens, q_rank] and
 // cache: [blocks, 1, 64, rank + rot], both of `dtype`; weights of `w_dtype`. cos_t, sin_t:
-// fp32 [positions, rot / 2]. q_rank may be 0 (no query latent).
+// fp32 [positions, rot / 2]. q_rank may be 0 (no query latent). interleaved: the rotation
+// pairs (2i, 2i + 1) instead of (i, i + rot / 2).
 SAKV_EXPORT int sakv_latent_prepare(const float* down, long long stride, int q_rank, int rank,
                                     int rot, const void* q_weight, const void* kv_weight,
                                     int w_dtype, float eps, const int32_t* positions,
                                     const int32_t* token_seq, const int32_t* block_table,
                                     int max_blocks, const float* cos_t, const float* sin_t,
                                     void* q_latent, void* cache, int dtype, int write_cache,
-                                    int tokens, cudaStream_t stream) {
+                                    int interleaved, int tokens, cudaStream_t stream) {
   if (tokens < 0 || q_rank < 0 || rank <= 0 || rot <= 0 || rot % 2 || max_blocks <= 0 ||
       stride < q_rank + rank + rot || w_dtype != dtype)
     return cudaErrorInvalidValue;
@@ -108,12 +114,12 @@ SAKV_EXPORT int sakv_latent_prepare(const float* down, long long stride, int q_r
   if (dtype == SAKV_F32)
     return prepare<float, float>(down, stride, q_rank, rank, rot, q_weight, kv_weight, eps,
                                  positions, token_seq, block_table, max_blocks, cos_t, sin_t,
-                                 q_latent, cache, write_cache, tokens, stream);
+                                 q_latent, cache, write_cache, interleaved, tokens, stream);
   if (dtype == SAKV_BF16)
     return prepare<__nv_bfloat16, __nv_bfloat16>(down, stride, q_rank, rank, rot, q_weight,
                                                  kv_weight, eps, positions, token_seq, block_table,
                                                  max_blocks, cos_t, sin_t, q_latent, cache,
-                                                 write_cache, tokens, stream);
+                                                 write_cache, interleaved, tokens, stream);
   return cudaErrorInvalidValue;
 }
 
@@ -121,8 +127,8 @@ SAKV_EXPORT int sakv_latent_prepare(const float* down, long long stride, int q_r
 // offset on are rotated in place by the token's position.
 SAKV_EXPORT int sakv_rotate_heads(void* x, int dtype, long long stride, int head_stride,
                                   int offset, int heads, int rot, const int32_t* positions,
-                                  const float* cos_t, const float* sin_t, int tokens,
-                                  cudaStream_t stream) {
+                                  const float* cos_t, const float* sin_t, int interleaved,
+                                  int tokens, cudaStream_t stream) {
   if (tokens < 0 || heads <= 0 || rot <= 0 || rot % 2 || offset < 0 || offset + rot > head_stride ||
       (long long)heads * head_stride > stride)
     return cudaErrorInvalidValue;
@@ -131,10 +137,11 @@ SAKV_EXPORT int sakv_rotate_heads(void* x, int dtype, long long stride, int head
   const dim3 grid(grid_for(count, 256)), block(256);
   if (dtype == SAKV_F32)
     return launch_ordered(rotate_heads_kernel<float>, grid, block, 0, stream, (float*)x, stride,
-                          head_stride, offset, heads, rot, positions, cos_t, sin_t, count);
+                          head_stride, offset, heads, rot, positions, cos_t, sin_t, count,
+                          interleaved);
   if (dtype == SAKV_BF16)
     return launch_ordered(rotate_heads_kernel<__nv_bfloat16>, grid, block, 0, stream,
                           (__nv_bfloat16*)x, stride, head_stride, offset, heads, rot, positions,
-                          cos_t, sin_t, count);
+                          cos_t, sin_t, count, interleaved);
   return cudaErrorInvalidValue;
 }

@@ -1,7 +1,11 @@
 // A mixture of small gated feed-forwards, routed on the device.
 //
-//   route    a warp a token: the `top` largest router logits (ties: the lowest index), their
-//            sigmoids as weights, and the token's place among the rows of each chosen expert
+//   route    a warp a token: the `top` largest router scores (ties: the lowest index), the
+//            scores as weights, and the token's place among the rows of each chosen expert.
+//            A score is the sigmoid of the logit, or the softmax over all the router's
+//            outputs; a bias an output may be added for the choice only. Outputs beyond the
+//            experts that have weights are identity experts: they take no rows, and combine
+//            adds the token's own input times the weight for them
 //   plan     one block: where each expert's rows begin and which (expert, first row) every
 //            tile of `TM` rows of the grouped products covers
 //   gather   the experts' input rows, sorted by expert: x * weight (the weight multiplies an
@@ -44,21 +48,36 @@ __global__ void logits_kernel(const T* __restrict__ h, const float* __restrict__
   if (lane == 0) out[item] = sum;
 }
 
+// `experts`: the router's outputs; the first `real` of them have weights. softmax 0: the score
+// is sigmoid(z); 1: exp(z - max) / sum over all outputs. bias (null: none): added to the score
+// for the choice. Without a bias the sigmoid's order is the logits' own, and they are compared.
 __global__ void route_kernel(const float* __restrict__ logits, long long ld, int experts, int top,
                              int32_t* __restrict__ chosen, float* __restrict__ weights,
                              int32_t* __restrict__ counts, int32_t* __restrict__ rank,
-                             int tokens) {
+                             int tokens, int real, int softmax, const float* __restrict__ bias) {
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= tokens) return;
   const float* z = logits + t * ld;
+  float top_z = -INFINITY, total = 1.f;
+  if (softmax) {
+    for (int e = lane; e < experts; e += 32) top_z = fmaxf(top_z, z[e]);
+    top_z = warp_max(top_z);
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) sum += expf(z[e] - top_z);
+    total = warp_sum(sum);
+  }
+  auto score = [&](float logit) {
+    return softmax ? expf(logit - top_z) / total : 1.f / (1.f + expf(-logit));
+  };
+  const bool by_logit = !softmax && bias == nullptr;
   uint32_t taken = 0;                              // bit i: this lane's i-th expert is chosen
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int at = 0x7fffffff;
     for (int i = 0, e = lane; e < experts; ++i, e += 32) {
       if (taken >> i & 1) continue;
-      const float v = z[e];
+      const float v = by_logit ? z[e] : score(z[e]) + (bias ? bias[e] : 0.f);
       if (v > best || (at == 0x7fffffff && !(v != v))) {
         best = v;
         at = e;
@@ -77,8 +96,8 @@ __global__ void route_kernel(const float* __restrict__ logits, long long ld, int
     if ((at & 31) == lane) taken |= 1u << (at >> 5);
     if (lane == 0) {
       chosen[t * top + k] = at;
-      weights[t * top + k] = 1.f / (1.f + expf(-best));
-      rank[t * top + k] = atomicAdd(counts + at, 1);
+      weights[t * top + k] = score(z[at]);
+      rank[t * top + k] = at < real ? atomicAdd(counts + at, 1) : -1;
     }
   }
 }
@@ -120,6 +139,10 @@ __global__ void gather_kernel(const T* __restrict__ h, const int32_t* __restrict
                               int weight_input) {
   const long long pair = blockIdx.x;                // token * top + k
   const long long t = pair / top;
+  if (rank[pair] < 0) {                             // an identity expert: no row
+    if (threadIdx.x == 0) slot_of[pair] = -1;
+    return;
+  }
   const int slot = offsets[chosen[pair]] + rank[pair];
   const float w = weight_input ? weights[pair] : 1.f;
   if (threadIdx.x == 0) slot_of[pair] = slot;
@@ -320,18 +343,24 @@ __global__ void clamped_act_kernel(const T* __restrict__ gate_up, T* __restrict_
   }
 }
 
+template <typename T>
 __global__ void combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot_of,
                                const float* __restrict__ weights, int weight_output,
                                const float* __restrict__ shared, const float* __restrict__ gate,
                                long long gate_ld, float* __restrict__ out, int top, int width,
-                               long long count) {
+                               long long count, const T* __restrict__ h) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
        i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / width;
     const int c = static_cast<int>(i - t * width);
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
-      const float v = rows[(long long)slot_of[t * top + k] * width + c];
+      const int slot = slot_of[t * top + k];
+      if (slot < 0) {                               // an identity expert: the input itself
+        sum = fmaf(widen(h[i]), weights[t * top + k], sum);
+        continue;
+      }
+      const float v = rows[(long long)slot * width + c];
       sum += weight_output ? v * weights[t * top + k] : v;
     }
     if (shared) {
@@ -346,19 +375,22 @@ __global__ void combine_kernel(const float* __restrict__ rows, const int32_t* __
 
 SAKV_EXPORT int sakv_moe_tile_rows() { return TM; }
 
-// logits: fp32 [tokens, ld] (the first `experts` columns); counts: int32 [experts], zero on
-// entry (plan leaves it zero again). chosen, rank: int32 [tokens, top]; weights: fp32.
+// logits: fp32 [tokens, ld] (the first `experts` columns, of which the first `real` belong to
+// experts with weights and the rest to identity experts); counts: int32 [real], zero on entry
+// (plan leaves it zero again). chosen, rank: int32 [tokens, top] (rank -1: an identity
+// expert); weights: fp32. softmax: the score's kind; bias: fp32 [experts] or null.
 SAKV_EXPORT int sakv_moe_route(const float* logits, long long ld, int experts, int top,
                                int32_t* chosen, float* weights, int32_t* counts, int32_t* rank,
-                               int tokens, cudaStream_t stream) {
+                               int tokens, int real, int softmax, const float* bias,
+                               cudaStream_t stream) {
   if (tokens < 0 || experts <= 0 || experts > 1024 || top <= 0 || top > experts || top > 32 ||
-      ld < experts)
+      ld < experts || real < 0 || real > experts)
     return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
   const int threads = 128;
   const long long blocks = ((long long)tokens * 32 + threads - 1) / threads;
   return launch_ordered(route_kernel, dim3((unsigned)blocks), dim3(threads), 0, stream, logits, ld,
-                        experts, top, chosen, weights, counts, rank, tokens);
+                        experts, top, chosen, weights, counts, rank, tokens, real, softmax, bias);
 }
 
 // out[t, o] = sum_i h[t, i] w[o, i] in fp32: h [tokens, width] of `dtype`, w fp32 [outputs,
@@ -463,15 +495,23 @@ SAKV_EXPORT int sakv_clamped_act(const void* gate_up, void* out, int dtype, int 
 }
 
 // out[t] = sum_k rows[slot_of[t, k]] (* weights[t, k] if weight_output) + shared[t] *
-// sigmoid(gate[t * gate_ld]); shared and gate may be null.
+// sigmoid(gate[t * gate_ld]); shared and gate may be null. A choice with slot_of -1 (an
+// identity expert) adds h[t] * weights[t, k]; h: [tokens, width] of `h_dtype`.
 SAKV_EXPORT int sakv_moe_combine(const float* rows, const int32_t* slot_of, const float* weights,
                                  int weight_output, const float* shared, const float* gate,
                                  long long gate_ld, float* out, int tokens, int top, int width,
-                                 cudaStream_t stream) {
-  if (tokens < 0 || top <= 0 || width <= 0) return cudaErrorInvalidValue;
+                                 const void* h, int h_dtype, cudaStream_t stream) {
+  if (tokens < 0 || top <= 0 || width <= 0 || h == nullptr) return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
   const long long count = (long long)tokens * width;
-  return launch_ordered(combine_kernel, dim3(grid_for(count, 256)), dim3(256), 0, stream, rows,
-                        slot_of, weights, weight_output, shared, gate, gate_ld, out, top, width,
-                        count);
+  const dim3 grid(grid_for(count, 256)), block(256);
+  if (h_dtype == SAKV_F32)
+    return launch_ordered(combine_kernel<float>, grid, block, 0, stream, rows, slot_of, weights,
+                          weight_output, shared, gate, gate_ld, out, top, width, count,
+                          (const float*)h);
+  if (h_dtype == SAKV_BF16)
+    return launch_ordered(combine_kernel<__nv_bfloat16>, grid, block, 0, stream, rows, slot_of,
+                          weights, weight_output, shared, gate, gate_ld, out, top, width, count,
+                          (const __nv_bfloat16*)h);
+  return cudaErrorInvalidValue;
 }

@@ -308,6 +308,33 @@ __global__ void scan_carry_kernel(const W* __restrict__ a_log, float* __restrict
 // ---------------------------------------------------------------------------------------
 constexpr int kRun = 16;          // tokens brought into shared memory at a time
 
+// What shapes q, k and v on their way into shared memory: `act` 1 is silu of each element
+// (0: as projected); `rot` > 0 turns the first `rot` numbers of every head of q and k by the
+// token's position (pairs (i, i + rot / 2), tables [positions, rot / 2] that carry the
+// rotation's magnitude), after the activation; `k_scale` multiplies k after that.
+struct FadeInput {
+  int act;
+  int rot;
+  const int32_t* positions;
+  const float* cos_t;
+  const float* sin_t;
+  float k_scale;
+};
+
+__device__ __forceinline__ float fade_input(const float* __restrict__ head, int i, int pos,
+                                            const FadeInput& in) {
+  float x = in.act ? silu(head[i]) : head[i];
+  if (i < in.rot) {
+    const int half = in.rot >> 1;
+    const bool low = i < half;
+    const int pair = low ? i : i - half;
+    const float other = in.act ? silu(head[low ? i + half : pair]) : head[low ? i + half : pair];
+    const float c = in.cos_t[(long long)pos * half + pair], sn = in.sin_t[(long long)pos * half + pair];
+    x = low ? x * c - other * sn : x * c + other * sn;
+  }
+  return x;
+}
+
 // PHASE as in the selective scan: 0 walks a sequence's whole part of the step from the state in
 // its slot; 1 walks one run of `chunk_len` tokens from zero and leaves the end state in scratch
 // memory ([sequences, max_chunks, heads, vdim, dim]), without outputs; 2 walks a run from the
@@ -321,7 +348,7 @@ __global__ void decay_attention_kernel(const float* __restrict__ proj, long long
                                        const int32_t* __restrict__ slots, float* __restrict__ out,
                                        int heads, int dim, int vdim, int rs, int cols,
                                        int keep_state, int chunk_len, int max_chunks,
-                                       float* __restrict__ scratch) {
+                                       float* __restrict__ scratch, const FadeInput in) {
   extern __shared__ __align__(16) float shared[];
   const int padded = rs * RP;                       // dim rounded up to whole lanes
   float* qs = shared;                               // [kRun, padded]
@@ -352,15 +379,19 @@ __global__ void decay_attention_kernel(const float* __restrict__ proj, long long
     __syncthreads();
     for (int e = threadIdx.x; e < run * padded; e += blockDim.x) {
       const int tt = e / padded, i = e - tt * padded;
-      const float* row = proj + (long long)(t0 + tt) * stride + (long long)h * dim + i;
-      if (PHASE != 1) qs[e] = i < dim ? silu(row[q_off]) : 0.f;
-      ks[e] = i < dim ? silu(row[k_off]) : 0.f;
+      const float* row = proj + (long long)(t0 + tt) * stride + (long long)h * dim;
+      const int pos = in.rot ? in.positions[t0 + tt] : 0;
+      if (PHASE != 1) qs[e] = i < dim ? fade_input(row + q_off, i, pos, in) : 0.f;
+      ks[e] = i < dim ? fade_input(row + k_off, i, pos, in) * in.k_scale : 0.f;
     }
     for (int e = threadIdx.x; e < run * cols; e += blockDim.x) {
       const int tt = e / cols, i = e - tt * cols;
-      vs[e] = col0 + i < vdim
-                  ? silu(proj[(long long)(t0 + tt) * stride + v_off + (long long)h * vdim + col0 + i])
-                  : 0.f;
+      float v = 0.f;
+      if (col0 + i < vdim) {
+        v = proj[(long long)(t0 + tt) * stride + v_off + (long long)h * vdim + col0 + i];
+        if (in.act) v = silu(v);
+      }
+      vs[e] = v;
     }
     __syncthreads();
     for (int tt = 0; tt < run; ++tt) {
@@ -412,23 +443,40 @@ __global__ void decay_carry_kernel(const float* __restrict__ decay_less_one,
   if (keep_state) *home = s;
 }
 
-// out[t] = y[t] / sqrt(mean(y[t]^2) + eps) * w * sigmoid(gate[t]) * scale over the whole row
-// (all heads' outputs together). A block a token.
+// out[t] = y[t] / sqrt(mean(y[t]^2) + eps) * w * sigmoid(gate[t]) * scale. A block a token.
+// `group` == width: the mean over the whole row (all heads' outputs together); smaller: over
+// each run of `group` numbers (a head's outputs), a warp a run. `w` null: no weight.
+// `gate_silu`: the gate is `g * sigmoid(g)` instead of `sigmoid(g)`.
 template <typename W, typename C>
 __global__ void __launch_bounds__(256)
 norm_gate_kernel(const float* __restrict__ y, const W* __restrict__ w,
                  const float* __restrict__ gate, long long gate_stride, C* __restrict__ out,
-                 int width, float eps, float scale) {
+                 int width, int group, int gate_silu, float eps, float scale) {
   __shared__ float scratch[33];
   const long long t = blockIdx.x;
   const float* row = y + t * width;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
-  const float r = 1.f / sqrtf(block_sum(ss, scratch) / static_cast<float>(width) + eps);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = row[i] * r * widen(w[i]);
-    if (gate) v *= 1.f / (1.f + expf(-gate[t * gate_stride + i]));
+  auto finish = [&](int i, float r) {
+    float v = row[i] * r;
+    if (w) v *= widen(w[i]);
+    if (gate) {
+      const float g = gate[t * gate_stride + i];
+      v *= (gate_silu ? g : 1.f) / (1.f + expf(-g));
+    }
     out[t * width + i] = narrow<C>(v * scale);
+  };
+  if (group == width) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+    const float r = 1.f / sqrtf(block_sum(ss, scratch) / static_cast<float>(width) + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) finish(i, r);
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int g0 = warp * group; g0 < width; g0 += warps * group) {
+    float ss = 0.f;
+    for (int i = lane; i < group; i += 32) ss = fmaf(row[g0 + i], row[g0 + i], ss);
+    const float r = 1.f / sqrtf(warp_sum(ss) / static_cast<float>(group) + eps);
+    for (int i = lane; i < group; i += 32) finish(g0 + i, r);
   }
 }
 
@@ -592,16 +640,22 @@ SAKV_EXPORT int sakv_selective_scan(const void* x, int c_dtype, const float* dt,
 // (heads * dim) and v at v_off (heads * vdim); decay: fp32 [heads] holding `decay - 1` (the
 // state moves by `(decay - 1) S + k v^T`, so a decay close to 1 loses nothing to rounding);
 // state: fp32 [slots, heads, vdim, dim]. out: fp32 [tokens, heads * vdim] = S^T q after the
-// token's update.
+// token's update. act: 1 = silu of q, k, v (0: as they are). rot > 0: the first `rot` numbers
+// of every head of q and k are turned by positions[t] (int32 [tokens]) with the tables cos_t,
+// sin_t (fp32 [positions, rot / 2]); k_scale multiplies k afterwards.
 SAKV_EXPORT int sakv_decay_attention(const float* proj, long long stride, int q_off, int k_off,
                                      int v_off, const float* decay, float* state,
                                      const int32_t* cu_seqlens, const int32_t* slots, float* out,
                                      int tokens, int sequences, int heads, int dim, int vdim,
                                      int keep_state, int chunk_len, int max_chunks, float* scratch,
+                                     int act, int rot, const int32_t* positions,
+                                     const float* cos_t, const float* sin_t, float k_scale,
                                      cudaStream_t stream) {
-  if (tokens < 0 || sequences < 0 || heads <= 0 || dim <= 0 || dim > 256 || vdim <= 0)
+  if (tokens < 0 || sequences < 0 || heads <= 0 || dim <= 0 || dim > 256 || vdim <= 0 ||
+      rot < 0 || rot % 2 || rot > dim || (rot > 0 && (!positions || !cos_t || !sin_t)))
     return cudaErrorInvalidValue;
   if (tokens == 0 || sequences == 0) return 0;
+  const FadeInput in = {act, rot, positions, cos_t, sin_t, k_scale};
   const bool runs = chunk_len > 0;
   if (runs && (max_chunks <= 0 || scratch == nullptr ||
                (long long)sequences * max_chunks > 65535))
@@ -620,7 +674,7 @@ SAKV_EXPORT int sakv_decay_attention(const float* proj, long long stride, int q_
 #define SAKV_FADE(RP, PHASE)                                                                     \
   launch_ordered(decay_attention_kernel<RP, PHASE>, grid, dim3(cols * rs), smem, stream, proj,   \
                  stride, q_off, k_off, v_off, decay, state, cu_seqlens, slots, out, heads, dim,  \
-                 vdim, rs, cols, keep_state, chunk_len, max_chunks, scratch)
+                 vdim, rs, cols, keep_state, chunk_len, max_chunks, scratch, in)
 #define SAKV_FADE_ALL(RP)                                                                        \
   do {                                                                                           \
     if (!runs) return SAKV_FADE(RP, 0);                                                          \
@@ -640,16 +694,20 @@ SAKV_EXPORT int sakv_decay_attention(const float* proj, long long stride, int q_
 #undef SAKV_FADE
 }
 
-// y: fp32 [tokens, width]; w: [width] of `w_dtype`; gate: fp32 rows `gate_stride` apart (null:
-// none). out: [tokens, width] of `out_dtype`.
+// y: fp32 [tokens, width]; w: [width] of `w_dtype` (null: no weight); gate: fp32 rows
+// `gate_stride` apart (null: none), used as sigmoid(g), or g sigmoid(g) with `gate_silu`.
+// group: how many numbers share a root mean square (width: the whole row; it divides width).
+// out: [tokens, width] of `out_dtype`.
 SAKV_EXPORT int sakv_norm_gate(const float* y, const void* w, int w_dtype, const float* gate,
                                long long gate_stride, void* out, int out_dtype, int tokens,
-                               int width, float eps, float scale, cudaStream_t stream) {
-  if (tokens < 0 || width <= 0) return cudaErrorInvalidValue;
+                               int width, int group, int gate_silu, float eps, float scale,
+                               cudaStream_t stream) {
+  if (tokens < 0 || width <= 0 || group <= 0 || width % group) return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
 #define SAKV_NG(W, C)                                                                            \
   return launch_ordered(norm_gate_kernel<W, C>, dim3(tokens), dim3(256), 0, stream, y,           \
-                        (const W*)w, gate, gate_stride, (C*)out, width, eps, scale)
+                        (const W*)w, gate, gate_stride, (C*)out, width, group, gate_silu, eps,     \
+                        scale)
   if (w_dtype == SAKV_F32 && out_dtype == SAKV_F32) SAKV_NG(float, float);
   if (w_dtype == SAKV_BF16 && out_dtype == SAKV_BF16) SAKV_NG(__nv_bfloat16, __nv_bfloat16);
   if (w_dtype == SAKV_BF16 && out_dtype == SAKV_F32) SAKV_NG(__nv_bfloat16, float);

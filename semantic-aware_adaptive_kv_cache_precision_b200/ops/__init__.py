@@ -338,7 +338,8 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      out_scale: float = 1.0, eps: float = 0.0, gate_elem_off: int | None = None,
                      splits: int = 1, key_splits: int = 1, warp_stage: bool = False,
                      heads_first: bool = False, keep_first: int = 0,
-                     sink: torch.Tensor | None = None) -> torch.Tensor:
+                     sink: torch.Tensor | None = None,
+                     head_gate: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of every token of the step over its sequence's cache, in the general
     form of `csrc/attention_distance.cu`: scores, softmax weights and weighted sums in fp32.
 
@@ -351,7 +352,8 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     (the last w keys) or `chunk` (keys of the query's own run of c positions) or neither;
     with a window, `keep_first` k: the keys at positions below k stay visible to every later
     query. `sink` (fp32 [heads]): the softmax's denominator of head h also holds
-    `exp(sink[h])`. With one map the output is multiplied by `out_scale`. Two
+    `exp(sink[h])`. With one map the output is multiplied by `out_scale`, and with `head_gate`
+    ([T, heads] of q's type, any row stride) head h's by `sigmoid(head_gate[t, h])`. Two
     maps are combined as `a1 - lam * a2`, divided by their root mean square over vdim (+ eps),
     times `out_scale`, times the sigmoid of the `vdim` numbers that lie `gate_elem_off + h *
     vdim` elements after the token's first query. Returns [T, heads * vdim] of q's type.
@@ -363,8 +365,12 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     are ONE token's groups of heads and share every chunk of its keys through shared memory, so
     the rows are read once for all the token's heads; `key_splits` blocks a token then take
     contiguous shares of the chunks."""
-    require_cuda(q, k_cache, v_cache, positions, token_seq, block_table, q2, sink)
+    require_cuda(q, k_cache, v_cache, positions, token_seq, block_table, q2, sink, head_gate)
     tokens = q.shape[0]
+    _check(head_gate is None or (maps == 1 and head_gate.dtype == q.dtype and head_gate.dim() == 2
+                                 and head_gate.shape == (tokens, heads)
+                                 and head_gate.stride(1) == 1),
+           "head_gate: [T, heads] of q's type with contiguous rows, one map")
     _check(sink is None or (sink.dtype == torch.float32 and sink.shape == (heads,)
                             and sink.is_contiguous()), "sink: fp32 [heads]")
     _check(keep_first >= 0 and not (keep_first and chunk), "keep_first goes with a window")
@@ -410,7 +416,8 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
          float(scale), int(window) if window else 0, int(chunk) if chunk else 0, float(lam),
          float(out_scale), float(eps), -1 if gate_elem_off is None else int(gate_elem_off),
          int(splits), int(key_splits), ptr(scratch), floats, ptr(tickets), int(warp_stage),
-         int(heads_first), int(keep_first) if window else 0, ptr(sink))
+         int(heads_first), int(keep_first) if window else 0, ptr(sink), ptr(head_gate),
+         0 if head_gate is None else head_gate.stride(0))
     return out
 
 

@@ -37,7 +37,7 @@ SIGNATURES = {
                                 [P, I, L, I, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P]),
     "sakv_cached_attention": ("attention_distance",
                               [P, I, L, I, P, L, I, I, I, P, P, I, P, I, P, P, P, I, I, I, I, I, I,
-                               I, F, I, I, F, F, F, I, I, I, P, L, P, I, I, I, P, P]),
+                               I, F, I, I, F, F, F, I, I, I, P, L, P, I, I, I, P, P, L, P]),
     "sakv_rms_update": ("norm_update", [P, P, P, F, P, P, F, I, P, I, I, I, F, P]),
     "sakv_qk_prepare": ("qk_prepare", [P, L, I, I, I, P, P, I, F, P, P, I, P, P, P, I, P, P, P,
                                        I, I, I, I, I, I, I, P]),
@@ -48,19 +48,19 @@ SIGNATURES = {
                                                I, I, I, I, I, I, I, P, P, P, P, I, P]),
     "sakv_conv_step": ("recurrent_scan", [P, L, P, P, I, P, P, P, I, I, I, I, I, P]),
     "sakv_decay_attention": ("recurrent_scan", [P, L, I, I, I, P, P, P, P, P, I, I, I, I, I, I,
-                                                I, I, P, P]),
-    "sakv_norm_gate": ("recurrent_scan", [P, P, I, P, L, P, I, I, I, F, F, P]),
+                                                I, I, P, I, I, P, P, P, F, P]),
+    "sakv_norm_gate": ("recurrent_scan", [P, P, I, P, L, P, I, I, I, I, I, F, F, P]),
     "sakv_layer_norm": ("layer_norm", [P, P, P, P, P, I, P, I, I, I, F, P]),
     "sakv_latent_prepare": ("latent", [P, L, I, I, I, P, P, I, F, P, P, P, I, P, P, P, P, I, I, I,
-                                       P]),
-    "sakv_rotate_heads": ("latent", [P, I, L, I, I, I, I, P, P, P, I, P]),
+                                       I, P]),
+    "sakv_rotate_heads": ("latent", [P, I, L, I, I, I, I, P, P, P, I, I, P]),
     "sakv_moe_logits": ("moe", [P, I, P, P, I, I, I, P]),
-    "sakv_moe_route": ("moe", [P, L, I, I, P, P, P, P, I, P]),
+    "sakv_moe_route": ("moe", [P, L, I, I, P, P, P, P, I, I, I, P, P]),
     "sakv_moe_plan": ("moe", [P, P, P, P, P, I, I, P]),
     "sakv_moe_gather": ("moe", [P, I, P, P, P, P, P, P, I, I, I, I, P]),
     "sakv_moe_product": ("moe", [P, I, P, P, L, P, P, P, P, I, P, I, I, I, F, F, P]),
     "sakv_clamped_act": ("moe", [P, P, I, I, I, F, F, P]),
-    "sakv_moe_combine": ("moe", [P, P, P, I, P, P, L, P, I, I, I, P]),
+    "sakv_moe_combine": ("moe", [P, P, P, I, P, P, L, P, I, I, I, P, I, P]),
     "sakv_rmsnorm": ("norm", [P, P, I, L, P, P, I, P, I, I, I, F, P]),
     "sakv_rope_store": ("rope", [P, I, L, P, P, P, I, P, P, I, P, P, I, I, I, I, I, P]),
     "sakv_attention_plain": ("attention_plain",

@@ -42,11 +42,19 @@ def router_logits(h: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def route(logits: torch.Tensor, experts: int, top: int) -> Routing:
-    """logits: fp32 [T, >= experts]; the `top` largest of the first `experts` columns a row."""
-    require_cuda(logits)
+def route(logits: torch.Tensor, experts: int, top: int, identity: int = 0,
+          softmax: bool = False, bias: torch.Tensor | None = None) -> Routing:
+    """logits: fp32 [T, >= experts + identity]; the `top` largest scores among the first
+    `experts + identity` columns a row. The score is the sigmoid of the logit, or with
+    `softmax` the softmax over those columns; `bias` (fp32 [experts + identity]) is added for
+    the choice only. A choice among the last `identity` columns is an identity expert: it gets
+    no row in the grouped products, and `combine` adds the token's input times its weight."""
+    require_cuda(logits, bias)
+    outputs = experts + identity
     _check(logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
-           and logits.shape[1] >= experts, "logits: fp32 [T, >= experts]")
+           and logits.shape[1] >= outputs, "logits: fp32 [T, >= experts + identity]")
+    _check(bias is None or (bias.dtype == torch.float32 and bias.shape == (outputs,)
+                            and bias.is_contiguous()), "bias: fp32 [experts + identity]")
     tokens, dev = logits.shape[0], logits.device
     key = (dev, experts)
     counts = _counts.get(key)
@@ -62,8 +70,8 @@ def route(logits: torch.Tensor, experts: int, top: int) -> Routing:
     r.offsets, r.n_tiles = plan[:experts + 1], plan[experts + 1:experts + 2]
     r.tile_expert = plan[experts + 2:experts + 2 + r.max_tiles]
     r.tile_row = plan[experts + 2 + r.max_tiles:]
-    call("sakv_moe_route", ptr(logits), logits.stride(0), experts, top, ptr(r.chosen),
-         ptr(r.weights), ptr(counts), ptr(r.rank), tokens)
+    call("sakv_moe_route", ptr(logits), logits.stride(0), outputs, top, ptr(r.chosen),
+         ptr(r.weights), ptr(counts), ptr(r.rank), tokens, experts, int(bool(softmax)), ptr(bias))
     call("sakv_moe_plan", ptr(counts), ptr(r.offsets), ptr(r.tile_expert), ptr(r.tile_row),
          ptr(r.n_tiles), experts, r.max_tiles)
     return r
@@ -115,12 +123,18 @@ def clamped_act(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tens
 
 
 def combine(products: torch.Tensor, r: Routing, weight_output: bool,
-            shared: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
+            shared: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+            h: torch.Tensor | None = None) -> torch.Tensor:
     """fp32 [T, width]: every token's rows of `products` (fp32 [T * top, width]) summed in the
     order of its choices (times their weights if `weight_output`), plus `shared` (fp32 [T,
-    width]) times `sigmoid(gate)` (`gate`: fp32 [T], may be strided; None: times 1)."""
-    require_cuda(products, shared, gate)
+    width]) times `sigmoid(gate)` (`gate`: fp32 [T], may be strided; None: times 1). `h` ([T,
+    width], the experts' input): what a chosen identity expert adds, times its weight."""
+    require_cuda(products, shared, gate, h)
     width = products.shape[1]
+    if h is None:
+        h = products            # (read only for identity experts, which then do not occur)
+    _check(h.is_contiguous() and h.shape[1] == width and h.shape[0] >= r.tokens,
+           "h: contiguous [T, width]")
     _check(products.dtype == torch.float32 and products.is_contiguous()
            and products.shape[0] == r.tokens * r.top, "products: fp32 [T * top, width]")
     _check(shared is None or (shared.dtype == torch.float32 and shared.is_contiguous()
@@ -130,17 +144,18 @@ def combine(products: torch.Tensor, r: Routing, weight_output: bool,
     out = torch.empty((r.tokens, width), dtype=torch.float32, device=products.device)
     call("sakv_moe_combine", ptr(products), ptr(r.slot_of), ptr(r.weights), int(weight_output),
          ptr(shared), ptr(gate), 0 if gate is None else gate.stride(0), ptr(out), r.tokens, r.top,
-         width)
+         width, ptr(h), dtype_code(h.dtype))
     return out
 
 
 def latent_prepare(down: torch.Tensor, q_rank: int, rank: int, rot: int,
                    q_weight: torch.Tensor | None, kv_weight: torch.Tensor, eps: float, step, view,
                    cos: torch.Tensor, sin: torch.Tensor, act_dtype: torch.dtype,
-                   write_cache: bool = True) -> torch.Tensor | None:
+                   write_cache: bool = True, interleaved: bool = False) -> torch.Tensor | None:
     """From the fused down projection `down` (fp32 [T, q_rank + rank + rot]): the normed query
     latent [T, q_rank] of `act_dtype` (None if q_rank is 0), and into the cache entry `view`
-    (keys [blocks, 1, 64, rank + rot]) the normed latent and the rotated shared key part."""
+    (keys [blocks, 1, 64, rank + rot]) the normed latent and the rotated shared key part
+    (pairs (i, i + rot/2); `interleaved`: (2i, 2i + 1))."""
     require_cuda(down, q_weight, kv_weight, cos, sin, view.keys)
     tokens = down.shape[0]
     _check(down.dtype == torch.float32 and down.dim() == 2 and down.stride(1) == 1
@@ -157,17 +172,19 @@ def latent_prepare(down: torch.Tensor, q_rank: int, rank: int, rot: int,
     call("sakv_latent_prepare", ptr(down), down.stride(0), q_rank, rank, rot, ptr(q_weight),
          ptr(kv_weight), dtype_code(act_dtype), float(eps), ptr(step.positions),
          ptr(step.token_seq), ptr(view.block_table), view.block_table.shape[1], ptr(cos), ptr(sin),
-         ptr(q_latent), ptr(keys), dtype_code(act_dtype), int(write_cache), tokens)
+         ptr(q_latent), ptr(keys), dtype_code(act_dtype), int(write_cache), int(interleaved),
+         tokens)
     return q_latent
 
 
 def rotate_heads(x: torch.Tensor, head_stride: int, offset: int, heads: int, rot: int,
-                 positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+                 positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                 interleaved: bool = False) -> None:
     """In place: in every head of every row of `x`, the `rot` columns from `offset` on are
-    rotated by the row's position (pairs (i, i + rot/2))."""
+    rotated by the row's position (pairs (i, i + rot/2); `interleaved`: (2i, 2i + 1))."""
     require_cuda(x, positions, cos, sin)
     _check(x.dim() == 2 and x.stride(1) == 1, "x: [T, columns] with contiguous rows")
     _check(cos.shape[1] == rot // 2 and cos.dtype == torch.float32 and cos.is_contiguous()
            and sin.is_contiguous(), "cos, sin: fp32 [positions, rot/2]")
     call("sakv_rotate_heads", ptr(x), dtype_code(x.dtype), x.stride(0), head_stride, offset, heads,
-         rot, ptr(positions), ptr(cos), ptr(sin), x.shape[0])
+         rot, ptr(positions), ptr(cos), ptr(sin), int(interleaved), x.shape[0])

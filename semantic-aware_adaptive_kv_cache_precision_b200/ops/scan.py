@@ -133,13 +133,25 @@ def _runs(run: int, step, state_size: int, sum_size: int, device):
 
 def decay_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, dim: int,
                     vdim: int, decay_less_one: torch.Tensor, state: torch.Tensor, step,
-                    keep_state: bool = True, run: int = 0) -> torch.Tensor:
+                    keep_state: bool = True, run: int = 0, activation: bool = True,
+                    cos: torch.Tensor | None = None, sin: torch.Tensor | None = None,
+                    key_scale: float = 1.0) -> torch.Tensor:
     """`S <- decay[h] S + k v^T; o = S^T q` a head over each sequence's tokens, with q, k, v =
     silu of the columns of fp32 `proj` from `q_off`, `k_off` (heads * dim each) and `v_off`
-    (heads * vdim). `decay_less_one`: fp32 [heads] holding `decay - 1` (the kernel adds `(decay - 1) S + k
+    (heads * vdim), or those columns as they are (`activation` False). With `cos`, `sin` (fp32
+    [positions, rot / 2]) the first rot numbers of every head of q and k are turned by the
+    token's position (pairs (i, i + rot / 2)); `key_scale` multiplies k after that.
+    `decay_less_one`: fp32 [heads] holding `decay - 1` (the kernel adds `(decay - 1) S + k
     v^T` to S). `state`: fp32 [slots, heads, vdim, dim] (the state's transpose), read and (with
     `keep_state`) left. `run`: as in `selective_scan`. Returns fp32 [T, heads * vdim]."""
-    require_cuda(proj, decay_less_one, state)
+    require_cuda(proj, decay_less_one, state, cos, sin)
+    rot = 0
+    if cos is not None:
+        _check(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32
+               and cos.dim() == 2 and cos.is_contiguous() and sin.is_contiguous()
+               and cos.shape == sin.shape and 2 * cos.shape[1] <= dim,
+               "cos, sin: fp32 [positions, rot / 2] with rot <= dim")
+        rot = 2 * cos.shape[1]
     tokens = proj.shape[0]
     _check(proj.dtype == torch.float32 and proj.dim() == 2 and proj.stride(1) == 1
            and max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim) <= proj.shape[1],
@@ -153,22 +165,30 @@ def decay_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, head
     call("sakv_decay_attention", ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off),
          ptr(decay_less_one), ptr(state), ptr(step.cu_seqlens), ptr(step.slots), ptr(out), tokens,
          step.sequences, heads, dim, vdim, int(keep_state), int(run) if runs else 0, runs,
-         ptr(scratch))
+         ptr(scratch), int(bool(activation)), rot, ptr(step.positions) if rot else None, ptr(cos),
+         ptr(sin), float(key_scale))
     return out
 
 
-def norm_gate(y: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | None, eps: float,
-              scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+def norm_gate(y: torch.Tensor, weight: torch.Tensor | None, gate: torch.Tensor | None, eps: float,
+              scale: float, out_dtype: torch.dtype, group: int | None = None,
+              gate_silu: bool = False) -> torch.Tensor:
     """`y / sqrt(mean(y^2) + eps) * weight * sigmoid(gate) * scale` over whole rows of fp32 `y`
-    [T, width]; `gate`: fp32 [T, width] (a view with any row stride) or None."""
+    [T, width], or with `group` over each run of that many numbers of a row (a head's
+    outputs); `weight` None: no weight; `gate`: fp32 [T, width] (a view with any row stride)
+    or None, used as `gate * sigmoid(gate)` with `gate_silu`."""
     require_cuda(y, weight, gate)
     tokens, width = y.shape
+    group = width if group is None else int(group)
     _check(y.dtype == torch.float32 and y.is_contiguous(), "y: contiguous fp32 [T, width]")
-    _check(weight.shape == (width,) and weight.is_contiguous(), "weight: [width]")
+    _check(weight is None or (weight.shape == (width,) and weight.is_contiguous()),
+           "weight: [width]")
+    _check(group > 0 and width % group == 0, "group: a divisor of the width")
     _check(gate is None or (gate.dtype == torch.float32 and gate.shape == y.shape
                             and gate.stride(1) == 1), "gate: fp32 [T, width] with contiguous rows")
     out = torch.empty((tokens, width), dtype=out_dtype, device=y.device)
-    call("sakv_norm_gate", ptr(y), ptr(weight), dtype_code(weight.dtype), ptr(gate),
+    call("sakv_norm_gate", ptr(y), ptr(weight),
+         dtype_code(weight.dtype if weight is not None else torch.float32), ptr(gate),
          0 if gate is None else gate.stride(0), ptr(out), dtype_code(out_dtype), tokens, width,
-         float(eps), float(scale))
+         group, int(bool(gate_silu)), float(eps), float(scale))
     return out

@@ -3,7 +3,7 @@ feed-forwards and their arrangement in a block."""
 
 from .base import Part, build_part, register_part
 from .norm import LayerNorm, RMSNorm
-from .rotary import NoPosition, RotaryHalf
+from .rotary import NoPosition, RotaryHalf, RotaryInterleaved
 from .attention import GQAAttention
 from .mlp import DenseMLP, GatedMLP
 from .block import PreNormBlock
@@ -20,7 +20,7 @@ from .parallel_mixer import ParallelMixer
 from .selective_scan import SelectiveScanMixer
 from .output_norm import OutputNormBlock
 
-__all__ = ["Part", "build_part", "register_part", "RMSNorm", "RotaryHalf", "NoPosition",
+__all__ = ["Part", "build_part", "register_part", "RMSNorm", "RotaryHalf", "RotaryInterleaved", "NoPosition",
            "GQAAttention", "GatedMLP", "DenseMLP", "PreNormBlock", "DeltaRuleMixer",
            "LogDistanceAttention", "StreamBlock", "StreamUpdate", "LayerNorm", "LatentAttention",
            "DifferentialAttention", "RoutedExperts", "SandwichBlock", "NormedUpdate",

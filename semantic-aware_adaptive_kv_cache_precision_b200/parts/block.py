@@ -14,9 +14,15 @@ class PreNormBlock(Part):
         p = spec.prefix
         self.mixer_norm = build_part(spec.mixer_norm, p + spec.mixer_norm_name, mode)
         self.mixer = build_part(spec.mixer, p + spec.mixer_name + ".", mode)
-        self.ffn_norm = build_part(spec.ffn_norm, p + spec.ffn_norm_name, mode)
-        self.ffn = build_part(spec.ffn, p + spec.ffn_name + ".", mode)
-        self.parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        self.ffn = self.ffn_norm = None
+        self.parts = (self.mixer_norm, self.mixer)
+        if spec.ffn is not None:       # (a layer may have no feed-forward)
+            self.ffn_norm = build_part(spec.ffn_norm, p + spec.ffn_norm_name, mode)
+            self.ffn = build_part(spec.ffn, p + spec.ffn_name + ".", mode)
+            self.parts += (self.ffn_norm, self.ffn)
+        self.kernel_libraries = tuple(dict.fromkeys(
+            ["norm"] + [name for part in self.parts
+                        for name in getattr(part, "kernel_libraries", ())]))
         self.graph_safe = all(getattr(part, "graph_safe", True) for part in self.parts)
 
     def tensor_decls(self):
@@ -42,11 +48,13 @@ class PreNormBlock(Part):
 
     def forward(self, x, step, view, write_cache=True, pending=None, leave_pending=True):
         h = _normed(self.mixer_norm, x, pending)
-        if getattr(self.mixer, "can_defer", False):
+        if getattr(self.mixer, "can_defer", False) and (self.ffn is not None or leave_pending):
             pending = self.mixer.forward(h, step, view, x, write_cache, defer=True)
         else:
             self.mixer.forward(h, step, view, x, write_cache)
             pending = None
+        if self.ffn is None:
+            return pending
         h = _normed(self.ffn_norm, x, pending)
         if leave_pending and getattr(self.ffn, "can_defer", False):
             return self.ffn.forward(h, step, x, defer=True)

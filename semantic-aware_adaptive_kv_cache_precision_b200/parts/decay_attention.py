@@ -11,6 +11,14 @@ cache as fixed-size per-sequence state, stored as its transpose [heads, value_di
 state moves by its change, `S += (decay - 1) S + k v^T`, with `decay - 1` rounded once from the
 exact number; in bfloat16 a long part of a prompt is walked in runs of `RUN` tokens side by side.
 
+The spec's fields turn this into its relatives: no activation on q, k, v; the first numbers of
+every head of q and k turned by the token's position (the tables of a `RotaryHalf`, rotation in
+fp32 as the rows enter the recurrence); k multiplied by a constant after that; the root mean
+square taken a head instead of over all heads, with or without a weight; `silu` instead of
+`sigmoid` for the gate. With all of them: retention,
+
+    q, k <- turn(q), turn(k) * dim^(-1/2);   o_h <- o_h / rms(o_h);   out = Wo [ o * silu(g) ]
+
 The part is a mixer of its own (`produce`) and a branch of a `ParallelMixer`.
 """
 
@@ -21,7 +29,7 @@ import torch
 from .. import ops
 from ..cache.needs import StateNeed
 from ..weights.decl import TensorDecl
-from .base import Part, register_part
+from .base import Part, build_part, register_part
 
 
 #: tokens a run when a long prompt is walked in runs side by side
@@ -38,6 +46,16 @@ class DecayAttention(Part):
             raise ValueError(f"head_dim {s.head_dim}: the recurrence kernel takes up to 256")
         if len(s.decay) != s.heads:
             raise ValueError(f"{len(s.decay)} decays for {s.heads} heads")
+        if s.activation not in (None, "silu") or s.norm not in ("all", "head") \
+                or s.gate_kind not in ("sigmoid", "silu"):
+            raise ValueError(f"activation {s.activation!r}, norm {s.norm!r} or gate "
+                             f"{s.gate_kind!r} is not built")
+        self.position = None
+        if s.position is not None:
+            if s.position.kind != "rotary_half" or s.position.rotary_dim > s.head_dim:
+                raise ValueError("the recurrence kernel turns pairs (i, i + dims / 2) of the "
+                                 "first dims <= head_dim numbers of a head")
+            self.position = build_part(s.position, prefix, mode)
         self.qk_cols = s.heads * s.head_dim
         self.v_cols = s.heads * s.value_dim
         self.decay_less_one = None
@@ -60,15 +78,16 @@ class DecayAttention(Part):
 
     def other_decls(self):
         s, p = self.spec, self.prefix
-        return [TensorDecl(p + "norm", (self.v_cols,), init="ones_normal"),
-                TensorDecl(p + "o", (s.hidden, self.v_cols))]
+        norm = [TensorDecl(p + "norm", (self.v_cols,), init="ones_normal")] if s.norm_weight else []
+        return norm + [TensorDecl(p + "o", (s.hidden, self.v_cols))]
 
     def input_bias(self, arena):
         return None
 
     def bind_rest(self, arena):
         p = self.prefix
-        self.norm_w, self.w_o = arena.view(p + "norm"), arena.view(p + "o")
+        self.norm_w = arena.view(p + "norm") if self.spec.norm_weight else None
+        self.w_o = arena.view(p + "o")
         # the kernel takes `decay - 1`, rounded to fp32 once from the exact number
         self.decay_less_one = (torch.tensor(self.spec.decay, dtype=torch.float64) - 1.0).to(
             device=self.w_o.device, dtype=torch.float32)
@@ -79,11 +98,20 @@ class DecayAttention(Part):
         `out_scale` included."""
         s = self.spec
         k_off, v_off = offset + self.qk_cols, offset + 2 * self.qk_cols
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.cos, self.position.sin
+            if step.max_position >= cos.shape[0]:
+                raise ValueError(f"position {step.max_position} is beyond the rotary table of "
+                                 f"{cos.shape[0]} positions")
         y = ops.decay_attention(proj, offset, k_off, v_off, s.heads, s.head_dim, s.value_dim,
                                 self.decay_less_one, view.state, step, keep_state=write_cache,
-                                run=self._run(step))
+                                run=self._run(step), activation=s.activation == "silu",
+                                cos=cos, sin=sin, key_scale=s.key_scale)
         gate = proj[:, v_off + self.v_cols:v_off + 2 * self.v_cols] if s.gate else None
-        return ops.norm_gate(y, self.norm_w, gate, s.eps, s.out_scale, self.act_dtype)
+        return ops.norm_gate(y, self.norm_w, gate, s.eps, s.out_scale, self.act_dtype,
+                             group=s.value_dim if s.norm == "head" else None,
+                             gate_silu=s.gate_kind == "silu")
 
     # -- the part alone ---------------------------------------------------------------------
 
@@ -105,6 +133,10 @@ class DecayAttention(Part):
             return 0
         return RUN
 
+    def prepare(self, device, max_positions):
+        if self.position is not None:
+            self.position.prepare(device, max_positions)
+
     def cache_need(self):
         s = self.spec
         return StateNeed((s.heads, s.value_dim, s.head_dim), "float32")
@@ -116,7 +148,9 @@ class DecayAttention(Part):
                           out_dtype=torch.float32)
 
     def forward(self, h, step, view, residual, write_cache=True):
-        ops.add_into(residual, self.produce(h, step, view, write_cache))
+        proj = ops.linear(h, self.w_in, out_dtype=torch.float32)
+        ops.linear(self.mix(proj, 0, h, step, view, write_cache), self.w_o,
+                   accumulate_into=residual)
 
 
 register_part("decay_attention", DecayAttention)

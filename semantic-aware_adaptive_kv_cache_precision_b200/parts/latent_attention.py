@@ -5,6 +5,11 @@
     q_h = [qp_h | rotate(qr_h)] = cq Wuq_h^T           (head_dim plain, rot_dim rotated)
     s_ij = (qp_h . Wuk_h c_j + qr_h . kr_j) * scale;   out_h = Wuv_h sum_j softmax(s)_ij c_j
 
+With a `window` w the sum runs over 0 <= i - j < w only (and the cache gives back the blocks
+behind it); with `sink` the softmax's denominator of head h also holds exp(sink_h); with
+`head_gate` out_h is multiplied by sigmoid(Wg h)_h, whose rows lie behind the query's in one
+product. The rotation pairs halves or neighbours, as the position part says.
+
 The keys and values of a head are never made: since `qp_h . (Wuk_h c) = (Wuk_h^T qp_h) . c`,
 each head's plain query is carried into the latent's space (a batched product over the heads),
 attention runs with one shared key row [c | kr] a position for all heads and returns weighted
@@ -49,7 +54,12 @@ class LatentAttention(Part):
             decls += [TensorDecl(p + "dq.norm", (s.q_rank,), init="ones_normal"),
                       TensorDecl(p + "uq", (s.heads * self.q_width, s.q_rank))]
         else:
-            decls.append(TensorDecl(p + "q", (s.heads * self.q_width, s.hidden)))
+            decls.append(TensorDecl(p + "q", (s.heads * self.q_width, s.hidden), group=p + "up"))
+        if s.head_gate:            # behind the queries' rows: one product makes both
+            decls.append(TensorDecl(p + "g", (s.heads, s.q_rank or s.hidden),
+                                    group=None if s.q_rank else p + "up"))
+        if s.sink:
+            decls.append(TensorDecl(p + "sink", (s.heads,)))
         decls += [TensorDecl(p + "dkv.norm", (s.kv_rank,), init="ones_normal"),
                   TensorDecl(p + "uk", (s.heads * s.head_dim, s.kv_rank)),
                   TensorDecl(p + "uv", (s.heads * s.value_dim, s.kv_rank)),
@@ -65,6 +75,15 @@ class LatentAttention(Part):
         # (the small tensors below take the activations' type whatever the checkpoint's)
         self.q_norm = arena.view(p + "dq.norm").to(self.act_dtype) if s.q_rank else None
         self.w_q = arena.view(p + ("uq" if s.q_rank else "q"))
+        self.w_gate = None
+        if s.head_gate:
+            if s.q_rank:
+                raise ValueError("a gate a head beside a query latent is not built")
+            both = arena.group_view(p + "up")
+            if both is None:
+                both = torch.cat([self.w_q, arena.view(p + "g")])
+            self.w_q = both        # [queries; gates]
+        self.sink = arena.view(p + "sink").float().contiguous() if s.sink else None
         self.kv_norm = arena.view(p + "dkv.norm").to(self.act_dtype)
         # [heads, kv_rank, head_dim]: the rows of Wuk_h^T, which carry a plain query to the
         # latent's space (a small copy, made once)
@@ -78,10 +97,15 @@ class LatentAttention(Part):
 
     def cache_need(self):
         s = self.spec
-        return KVNeed(1, s.kv_rank + s.rot_dim, None, value_dim=0)
+        return KVNeed(1, s.kv_rank + s.rot_dim, s.window, value_dim=0)
 
     def produce(self, h, step, view, write_cache=True):
         """The mixer's output, fp32 [T, hidden]."""
+        return ops.linear(self._heads(h, step, view, write_cache), self.w_o,
+                          out_dtype=torch.float32)
+
+    def _heads(self, h, step, view, write_cache):
+        """The heads' outputs side by side, [T, heads * value_dim]: the input of `w_o`."""
         s, pos = self.spec, self.position
         if step.max_position >= pos.cos.shape[0]:
             raise ValueError(f"position {step.max_position} is beyond the rotary table of "
@@ -91,23 +115,24 @@ class LatentAttention(Part):
         down = ops.linear(h, self.w_down, out_dtype=torch.float32)
         q_latent = ops.latent_prepare(down, q_rank, rank, s.rot_dim, self.q_norm, self.kv_norm,
                                       s.eps, step, view, pos.cos, pos.sin, self.act_dtype,
-                                      write_cache)
+                                      write_cache, pos.interleaved)
         q = ops.linear(q_latent if s.q_rank else h, self.w_q, out_dtype=self.act_dtype)
         ops.rotate_heads(q, self.q_width, s.head_dim, s.heads, s.rot_dim, step.positions,
-                         pos.cos, pos.sin)
-        q3 = q.view(tokens, s.heads, self.q_width)
+                         pos.cos, pos.sin, pos.interleaved)
+        q_cols = s.heads * self.q_width
+        q3 = q[:, :q_cols].view(tokens, s.heads, self.q_width)
         # every head's plain query in the latent's space
         in_latent = torch.empty((tokens, s.heads, rank), dtype=q.dtype, device=q.device)
         ops.per_head(q3[:, :, :s.head_dim], self.w_uk_t, in_latent)
         mixed = ops.cached_attention(
             in_latent, view.keys, None, step.positions, step.token_seq, view.block_table,
             s.heads, rank + s.rot_dim, rank, s.scale, q2=q3[:, :, s.head_dim:], q_split=rank,
-            **self._decode_form(step, q))
+            window=s.window, sink=self.sink,
+            head_gate=q[:, q_cols:] if s.head_gate else None, **self._decode_form(step, q))
         # the weighted sums of latents to each head's values
         heads_out = torch.empty((tokens, s.heads, s.value_dim), dtype=q.dtype, device=q.device)
         ops.per_head(mixed.view(tokens, s.heads, rank), self.w_uv, heads_out)
-        return ops.linear(heads_out.view(tokens, s.heads * s.value_dim), self.w_o,
-                          out_dtype=torch.float32)
+        return heads_out.view(tokens, s.heads * s.value_dim)
 
     def _decode_form(self, step, q) -> dict:
         """How a step's tokens share their keys. Prompts, and everything in the 32-bit mode:
@@ -119,11 +144,13 @@ class LatentAttention(Part):
         numbers as long as they do)."""
         if q.dtype == torch.float32 or not step.is_decode:
             return {}
-        return {"heads_first": True,
-                "key_splits": ops.plan_token_blocks(step.max_len_bound or step.max_len, step.tokens)}
+        keys = step.max_len_bound or step.max_len
+        if self.spec.window:         # (a window's first chunk and its last may both be partial)
+            keys = min(keys, self.spec.window + 63)
+        return {"heads_first": True, "key_splits": ops.plan_token_blocks(keys, step.tokens)}
 
     def forward(self, h, step, view, residual, write_cache=True):
-        ops.add_into(residual, self.produce(h, step, view, write_cache))
+        ops.linear(self._heads(h, step, view, write_cache), self.w_o, accumulate_into=residual)
 
 
 register_part("latent_attention", LatentAttention)

@@ -17,6 +17,9 @@ from .base import Part, register_part
 
 
 class RotaryHalf(Part):
+    #: which numbers of a head make a pair: False (i, i + rotary_dim / 2), True (2i, 2i + 1)
+    interleaved = False
+
     def __init__(self, spec, prefix, mode):
         super().__init__(spec, prefix, mode)
         if spec.rotary_dim % 2 or spec.rotary_dim > spec.head_dim or spec.rotary_dim <= 0:
@@ -81,6 +84,20 @@ class RotaryHalf(Part):
                        view.keys, view.values, heads, kv_heads, head_dim, write_cache)
 
 
+class RotaryInterleaved(RotaryHalf):
+    """The same table of angles for pairs of neighbours: dimension 2i turns with 2i + 1. The
+    kernels that take a rotation with an `interleaved` argument ask `position.interleaved`;
+    the kernel behind `rotate_store` pairs halves only."""
+
+    interleaved = True
+
+    def tables(self, step, head_dim):
+        return None
+
+    def rotate_store(self, qkv, step, view, heads, kv_heads, head_dim, write_cache=True):
+        raise NotImplementedError("rotate_store pairs (i, i + rotary_dim / 2) only")
+
+
 class NoPosition(Part):
     """No position encoding: keys and values go to the cache as they are."""
 
@@ -90,4 +107,5 @@ class NoPosition(Part):
 
 
 register_part("rotary_half", RotaryHalf)
+register_part("rotary_interleaved", RotaryInterleaved)
 register_part("no_position", NoPosition)

@@ -1,6 +1,8 @@
 """A mixture of clamped gated feed-forwards with a shared one (`RoutedExpertsSpec`):
 
-    z = h Wrouter^T (fp32);  s = sigmoid(z);  the `top` largest s choose a token's experts
+    z = h Wrouter^T (fp32);  s = sigmoid(z), or softmax(z) over all the router's outputs
+    the `top` largest s (+ a learned correction an output, for the choice only) choose a
+    token's experts; the last `identity` outputs stand for experts that return their input
     expert_e(x) = Wdown_e [ g * sigmoid(alpha g) * (u + 1) ],  g = min(Wgate_e x, limit),
                                                               u = clamp(Wup_e x, -limit, limit)
     out = sum_chosen expert_e(s_e h)  +  sigmoid(h Wsg^T) * shared(h)
@@ -29,12 +31,15 @@ class RoutedExperts(Part):
 
     def __init__(self, spec, prefix, mode):
         super().__init__(spec, prefix, mode)
-        if spec.score != "sigmoid":
-            raise ValueError(f"router score {spec.score!r}: only 'sigmoid' is built")
+        if spec.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"router score {spec.score!r}: 'sigmoid' and 'softmax' are built")
         if spec.renormalize:
             raise ValueError("renormalized router weights are not built")
-        if spec.top > spec.experts or spec.experts > 1024 or spec.top > 32:
-            raise ValueError("the router takes up to 1024 experts and top up to 32 <= experts")
+        self.outputs = spec.experts + spec.identity
+        if spec.experts < 1 or spec.identity < 0 or spec.top > self.outputs \
+                or self.outputs > 1024 or spec.top > 32:
+            raise ValueError("the router takes up to 1024 outputs (experts and identity "
+                             "experts) and top up to 32 of them")
 
     def tensor_decls(self):
         s, p = self.spec, self.prefix
@@ -44,7 +49,9 @@ class RoutedExperts(Part):
                             ("down", (s.hidden, ff))):
             decls += [TensorDecl(f"{p}e{e}.{name}", shape, group=f"{p}experts.{name}")
                       for e in range(s.experts)]
-        decls.append(TensorDecl(p + "router", (s.experts, s.hidden), group=p + "route"))
+        decls.append(TensorDecl(p + "router", (self.outputs, s.hidden), group=p + "route"))
+        if s.correction:
+            decls.append(TensorDecl(p + "correction", (self.outputs,)))
         if s.shared is not None:
             fs = s.shared.intermediate
             if s.shared_gate:
@@ -73,6 +80,8 @@ class RoutedExperts(Part):
             route.append(arena.view(p + "shared.sg"))
         # the router's product is 32-bit in both modes: its rows are kept widened
         self.w_route = torch.cat(route).float().contiguous()
+        self.correction = arena.view(p + "correction").float().contiguous() if s.correction \
+            else None
         if s.shared is not None:
             self.w_shared_in = arena.group_view(p + "shared.gate_up")
             if self.w_shared_in is None:
@@ -84,7 +93,8 @@ class RoutedExperts(Part):
         """The feed-forward's output, fp32 [T, hidden]."""
         s = self.spec
         logits = mixture.router_logits(h, self.w_route)
-        routing = mixture.route(logits, s.experts, s.top)
+        routing = mixture.route(logits, s.experts, s.top, s.identity, s.score == "softmax",
+                                self.correction)
         # (a checkpoint stored in 32 bits keeps its matrices so: the experts then run in 32 bits)
         rows = mixture.gather_rows(h if h.dtype == self.w_gate.dtype else h.to(self.w_gate.dtype),
                                    routing, s.weight_input)
@@ -96,8 +106,8 @@ class RoutedExperts(Part):
             both = ops.linear(h, self.w_shared_in, out_dtype=self.act_dtype)
             shared = ops.linear(mixture.clamped_act(both, s.shared.limit, s.shared.alpha),
                                 self.w_shared_down, out_dtype=torch.float32)
-            gate = logits[:, s.experts] if self.has_gate else None
-        return mixture.combine(products, routing, not s.weight_input, shared, gate)
+            gate = logits[:, self.outputs] if self.has_gate else None
+        return mixture.combine(products, routing, not s.weight_input, shared, gate, h)
 
     def forward(self, h, step, residual):
         ops.add_into(residual, self.produce(h, step))

@@ -157,7 +157,9 @@ class WindowSinkAttention(Part):
                           out_dtype=torch.float32)
 
     def forward(self, h, step, view, residual, write_cache=True):
-        ops.add_into(residual, self.produce(h, step, view, write_cache))
+        proj = ops.linear(h, self.w_in, self.b_in, out_dtype=torch.float32)
+        ops.linear(self.mix(proj, 0, h, step, view, write_cache), self.w_o,
+                   accumulate_into=residual)
 
 
 register_part("window_sink_attention", WindowSinkAttention)
