@@ -247,7 +247,8 @@ def forward(config, tensors, ids, hidden_states=None):
 
 
 def generate(config, tensors, ids, new_tokens):
+    """The `new_tokens` tokens that greedy decoding adds to `ids`."""
     ids = list(ids)
     for _ in range(new_tokens):
         ids.append(int(np.argmax(forward(config, tensors, ids)[-1])))
-    return ids
+    return ids[len(ids) - new_tokens:]
