@@ -465,6 +465,117 @@ def venanex_rates(size, times, batch, context, tokens, hbm) -> dict:
     return out
 
 
+#: layer sizes for `--design gesuvik`: (width; retention heads x (dim, vdim); latent attention
+#: heads x (plain, rotated, value) sizes over a latent of kv_rank; attention heads / kv heads x
+#: (dim, vdim) with rot rotated numbers a head; the windows of both attentions; experts: count,
+#: identity experts, chosen, width, shared width)
+GESUVIK_SIZES = {
+    "1k": dict(width=1024, retention=(8, 128, 128), latent=(8, 128, 64, 128), kv_rank=512,
+               attention=(8, 2, 128, 128), rot=64, window=1024, experts=(16, 2, 2, 1024, 2048),
+               vocab=32768, layers=6),
+    "2k": dict(width=2048, retention=(16, 128, 128), latent=(16, 128, 64, 128), kv_rank=512,
+               attention=(16, 4, 128, 128), rot=64, window=2048, experts=(32, 4, 4, 1024, 4096),
+               vocab=32768, layers=6),
+}
+
+
+def gesuvik_configs(size: dict) -> dict:
+    """The Gesuvik config of a size: retention, latent attention, attention, twice, the second
+    latent layer with the first one's weights."""
+    rheads, rdim, rvdim = size["retention"]
+    heads, dim, rot_dim, vdim = size["latent"]
+    aheads, akv, adim, avdim = size["attention"]
+    experts, identity, top, ff, shared = size["experts"]
+    mlp = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top},
+           "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": shared, "limit": 7.0}}
+    kinds = {
+        "retention": {"heads": rheads, "dim": rdim, "vdim": rvdim,
+                      "decay": [1.0 - 2.0 ** -(5 + 6 * h / rheads) for h in range(rheads)],
+                      "rot": {"base": 1000000.0, "dims": rdim}},
+        "latent_attention": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim,
+                             "kv_rank": size["kv_rank"], "scale": (dim + rot_dim) ** -0.5,
+                             "mask": {"size": size["window"]},
+                             "rot": {"base": 10000.0, "dims": rot_dim}},
+        "attention": {"heads": aheads, "kv_heads": akv, "dim": adim, "vdim": avdim,
+                      "scale": adim ** -0.5, "mask": {"size": size["window"]},
+                      "rot": {"base": 1000000.0, "dims": size["rot"],
+                              "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0,
+                                          "slow": 1.0}}}}
+    layers = []
+    for i in range(size["layers"]):
+        kind = ("retention", "latent_attention", "attention")[i % 3]
+        entry = {"type": kind, "mixer": kinds[kind], "mlp": mlp}
+        if kind == "latent_attention" and i >= 3:
+            entry["weights_of"] = 1
+        layers.append(entry)
+    return {"architecture": "Gesuvik", "vocab": size["vocab"], "width": size["width"],
+            "norm": {"eps": 1e-6}, "logit_scale": 1.0, "logit_softcap": 30.0,
+            "initializer_range": 0.02, "layers": layers}
+
+
+def gesuvik_rates(size, gt, vt, vsize, batch, context, tokens, hbm) -> dict:
+    """What the design's own kernels must move or compute in the timed steps, against the
+    measured peaks, and the like figures of Venanex's kernels from the same run. `gt`, `vt`:
+    kernel times of Gesuvik and Venanex; `vsize`: Venanex's sizes."""
+    rheads, rdim, rvdim = size["retention"]
+    heads, dim, rot_dim, vdim = size["latent"]
+    aheads, akv, adim, avdim = size["attention"]
+    experts, identity, top, ff, shared = size["experts"]
+    n_each = size["layers"] // 3
+    rank, width, window = size["kv_rank"], size["width"], size["window"]
+
+    def of_hbm(nbytes, us):
+        return round(nbytes / (us * 1e-6) / 1e9 / hbm, 3) if us else None
+
+    def tflops(flops, us):
+        return round(flops / (us * 1e-6) / 1e12, 2) if us else None
+
+    out = {}
+    # retention over a prompt: q, k, v (fp32) in, o (fp32) out; a decode step: the state twice
+    qkv = rheads * (2 * rdim + rvdim)
+    out["retention_prefill_of_measured_hbm"] = of_hbm(
+        tokens * (qkv + rheads * rvdim) * 4 * n_each, gt["prefill"].get("decay_attention"))
+    out["retention_decode_of_measured_hbm"] = of_hbm(
+        batch * (rheads * rdim * rvdim * 4 * 2 + (qkv + rheads * rvdim) * 4) * n_each,
+        gt["decode"].get("decay_attention"))
+    # both attentions share one kernel: multiply-adds over the keys a query sees
+    keys = sum(min(i + 1, window) for i in range(tokens))
+    flops = 2.0 * keys * n_each * (heads * (2 * rank + rot_dim) + aheads * (adim + avdim))
+    out["attention_prefill_tflops_fp32"] = tflops(flops, gt["prefill"].get("cached_attention"))
+    seen = min(context, window)
+    out["attention_decode_of_measured_hbm"] = of_hbm(
+        batch * seen * 2 * n_each * ((rank + rot_dim) + akv * (adim + avdim)),
+        gt["decode"].get("cached_attention"))
+    moe_flops = 2.0 * tokens * top * experts / (experts + identity) * 3 * ff * width * size["layers"]
+    out["experts_prefill_tflops_bf16"] = tflops(moe_flops, gt["prefill"].get("moe_product"))
+    touched = min(batch * top, experts) * 3 * ff * width * 2 * size["layers"]
+    out["experts_decode_of_measured_hbm"] = of_hbm(touched, gt["decode"].get("moe_product"))
+    # the norm before each sublayer: x (fp32) in, h (bf16) out
+    out["rms_norm_prefill_of_measured_hbm"] = of_hbm(
+        tokens * width * (4 + 2) * 2 * size["layers"], gt["prefill"].get("rmsnorm"))
+    # the like kernels of Venanex, in the same run
+    vheads, vdim_, vrot, vv = vsize["latent"]
+    vah, vakv, vad, vavd = vsize["attention"]
+    ve, vtop, vff, _ = vsize["experts"]
+    n_att = sum(1 for i in range(vsize["layers"]) if i % 3 == 2)
+    n_lat = vsize["layers"] - n_att
+    pairs = tokens * (tokens + 1) // 2
+    chunk_pairs = sum(i % vsize["chunk"] + 1 for i in range(tokens))
+    flops = 2.0 * vheads * (2 * vsize["kv_rank"] + vrot) * pairs * n_lat + \
+        2.0 * vah * (2 * vad + 2 * vavd) * chunk_pairs * n_att
+    out["venanex_attention_prefill_tflops_fp32"] = tflops(flops, vt["prefill"].get("cached_attention"))
+    read = batch * 2 * (context * (vsize["kv_rank"] + vrot) * n_lat
+                        + min(context, vsize["chunk"]) * vakv * (2 * vad + vavd) * n_att)
+    out["venanex_attention_decode_of_measured_hbm"] = of_hbm(read, vt["decode"].get("cached_attention"))
+    out["venanex_experts_prefill_tflops_bf16"] = tflops(
+        2.0 * tokens * vtop * 3 * vff * vsize["width"] * vsize["layers"],
+        vt["prefill"].get("moe_product"))
+    out["venanex_experts_decode_of_measured_hbm"] = of_hbm(
+        min(batch * vtop, ve) * 3 * vff * vsize["width"] * 2 * vsize["layers"],
+        vt["decode"].get("moe_product"))
+    return out
+
+
 #: layer sizes for `--design zodirax`: (width, selective scan: inner, state, dt_rank, taps;
 #: window attention heads / kv heads x (dim, vdim) with window and kept first tokens, rotated
 #: numbers a head; fading-state attention heads x (dim, vdim); feed-forward)
@@ -721,6 +832,36 @@ def design_arm(args) -> int:
                           "batch": batch, "context": context, "prefill_tokens": tokens, "steps": K,
                           "warmup": W, "peaks": pk, "sizes": rows}))
         return 0
+    if args.design == "gesuvik":
+        for name in sizes:
+            size, vsize = GESUVIK_SIZES[name], VENANEX_SIZES[name]
+            gesuvik, venanex = gesuvik_configs(size), venanex_configs(vsize)[0]
+            row = {"size": name, **{k: size[k] for k in ("width", "layers", "retention", "latent",
+                                                         "kv_rank", "attention", "window",
+                                                         "experts")}}
+            kernels = {}
+            for label, config in (("venanex", venanex), ("gesuvik", gesuvik)):
+                engine, slots, prompt, out = measure(config)
+                row[label] = out
+                engine.close(slots)
+                engine.release()
+                del engine
+                torch.cuda.empty_cache()
+                engine, slots, prompt, _ = measure(config, graphs=False)
+                row[label + "_kernels_us"] = kernels[label] = kernel_times(engine, slots, prompt)
+                engine.close(slots)
+                engine.release()
+                del engine
+                torch.cuda.empty_cache()
+            row["kernel_rates"] = gesuvik_rates(size, kernels["gesuvik"], kernels["venanex"], vsize,
+                                                batch, context, tokens, hbm)
+            rows.append(row)
+        print(json.dumps({"design": "gesuvik", "beside": "venanex of equal width, depth, latent "
+                          "attention heads and experts", "dtype": "bf16",
+                          "data": "synthetic (random weights and tokens; weights larger than L2)",
+                          "batch": batch, "context": context, "prefill_tokens": tokens, "steps": K,
+                          "warmup": W, "peaks": pk, "sizes": rows}))
+        return 0
     if args.design == "zodirax":
         for name in sizes:
             size = ZODIRAX_SIZES[name]
@@ -806,7 +947,7 @@ def design_arm(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["tebonex", "venanex", "zodirax"],
+    ap.add_argument("--design", default=None, choices=["tebonex", "venanex", "zodirax", "gesuvik"],
                     help="instead of the default workload: the named design at layer sizes "
                          "that resemble real models, beside the Qwen2 decoder of equal size")
     ap.add_argument("--design-sizes", default="1k,2k", help="which of: " + ", ".join(DESIGN_SIZES))

@@ -348,7 +348,7 @@ __global__ void combine_kernel(const float* __restrict__ rows, const int32_t* __
                                const float* __restrict__ weights, int weight_output,
                                const float* __restrict__ shared, const float* __restrict__ gate,
                                long long gate_ld, float* __restrict__ out, int top, int width,
-                               long long count, const T* __restrict__ h) {
+                               long long count, const T* __restrict__ h, int accumulate) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
        i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / width;
@@ -367,7 +367,7 @@ __global__ void combine_kernel(const float* __restrict__ rows, const int32_t* __
       const float s = gate ? 1.f / (1.f + expf(-gate[t * gate_ld])) : 1.f;
       sum = fmaf(shared[i], s, sum);
     }
-    out[i] = sum;
+    out[i] = accumulate ? out[i] + sum : sum;
   }
 }
 
@@ -496,11 +496,13 @@ SAKV_EXPORT int sakv_clamped_act(const void* gate_up, void* out, int dtype, int 
 
 // out[t] = sum_k rows[slot_of[t, k]] (* weights[t, k] if weight_output) + shared[t] *
 // sigmoid(gate[t * gate_ld]); shared and gate may be null. A choice with slot_of -1 (an
-// identity expert) adds h[t] * weights[t, k]; h: [tokens, width] of `h_dtype`.
+// identity expert) adds h[t] * weights[t, k]; h: [tokens, width] of `h_dtype`. accumulate:
+// out += the sum (the residual stream itself) instead of out = the sum.
 SAKV_EXPORT int sakv_moe_combine(const float* rows, const int32_t* slot_of, const float* weights,
                                  int weight_output, const float* shared, const float* gate,
                                  long long gate_ld, float* out, int tokens, int top, int width,
-                                 const void* h, int h_dtype, cudaStream_t stream) {
+                                 const void* h, int h_dtype, int accumulate,
+                                 cudaStream_t stream) {
   if (tokens < 0 || top <= 0 || width <= 0 || h == nullptr) return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
   const long long count = (long long)tokens * width;
@@ -508,10 +510,10 @@ SAKV_EXPORT int sakv_moe_combine(const float* rows, const int32_t* slot_of, cons
   if (h_dtype == SAKV_F32)
     return launch_ordered(combine_kernel<float>, grid, block, 0, stream, rows, slot_of, weights,
                           weight_output, shared, gate, gate_ld, out, top, width, count,
-                          (const float*)h);
+                          (const float*)h, accumulate);
   if (h_dtype == SAKV_BF16)
     return launch_ordered(combine_kernel<__nv_bfloat16>, grid, block, 0, stream, rows, slot_of,
                           weights, weight_output, shared, gate, gate_ld, out, top, width, count,
-                          (const __nv_bfloat16*)h);
+                          (const __nv_bfloat16*)h, accumulate);
   return cudaErrorInvalidValue;
 }

@@ -661,7 +661,7 @@ SAKV_EXPORT int sakv_decay_attention(const float* proj, long long stride, int q_
                (long long)sequences * max_chunks > 65535))
     return cudaErrorInvalidValue;
   const long long walks = runs ? (long long)sequences * max_chunks : sequences;
-  const int rp = dim <= 128 ? 4 : 8;
+  const int rp = dim < 128 ? 4 : 8;        // (rows a lane; 16 lanes a column from 128 rows on)
   const int rs = lanes_for(dim, rp);
   int cols = 256 / rs;                       // value columns a block
   // fewer columns a block while the step's heads and walks do not fill the GPU

@@ -60,7 +60,7 @@ SIGNATURES = {
     "sakv_moe_gather": ("moe", [P, I, P, P, P, P, P, P, I, I, I, I, P]),
     "sakv_moe_product": ("moe", [P, I, P, P, L, P, P, P, P, I, P, I, I, I, F, F, P]),
     "sakv_clamped_act": ("moe", [P, P, I, I, I, F, F, P]),
-    "sakv_moe_combine": ("moe", [P, P, P, I, P, P, L, P, I, I, I, P, I, P]),
+    "sakv_moe_combine": ("moe", [P, P, P, I, P, P, L, P, I, I, I, P, I, I, P]),
     "sakv_rmsnorm": ("norm", [P, P, I, L, P, P, I, P, I, I, I, F, P]),
     "sakv_rope_store": ("rope", [P, I, L, P, P, P, I, P, P, I, P, P, I, I, I, I, I, P]),
     "sakv_attention_plain": ("attention_plain",

@@ -124,12 +124,13 @@ def clamped_act(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tens
 
 def combine(products: torch.Tensor, r: Routing, weight_output: bool,
             shared: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-            h: torch.Tensor | None = None) -> torch.Tensor:
+            h: torch.Tensor | None = None, into: torch.Tensor | None = None) -> torch.Tensor:
     """fp32 [T, width]: every token's rows of `products` (fp32 [T * top, width]) summed in the
     order of its choices (times their weights if `weight_output`), plus `shared` (fp32 [T,
     width]) times `sigmoid(gate)` (`gate`: fp32 [T], may be strided; None: times 1). `h` ([T,
-    width], the experts' input): what a chosen identity expert adds, times its weight."""
-    require_cuda(products, shared, gate, h)
+    width], the experts' input): what a chosen identity expert adds, times its weight. `into`
+    (fp32 [T, width], the residual stream): the sum is added to it and it is returned."""
+    require_cuda(products, shared, gate, h, into)
     width = products.shape[1]
     if h is None:
         h = products            # (read only for identity experts, which then do not occur)
@@ -141,10 +142,13 @@ def combine(products: torch.Tensor, r: Routing, weight_output: bool,
                               and shared.shape == (r.tokens, width)), "shared: fp32 [T, width]")
     _check(gate is None or (gate.dtype == torch.float32 and gate.dim() == 1
                             and gate.shape[0] == r.tokens), "gate: fp32 [T]")
-    out = torch.empty((r.tokens, width), dtype=torch.float32, device=products.device)
+    _check(into is None or (into.dtype == torch.float32 and into.is_contiguous()
+                            and into.shape == (r.tokens, width)), "into: fp32 [T, width]")
+    out = into if into is not None else torch.empty((r.tokens, width), dtype=torch.float32,
+                                                    device=products.device)
     call("sakv_moe_combine", ptr(products), ptr(r.slot_of), ptr(r.weights), int(weight_output),
          ptr(shared), ptr(gate), 0 if gate is None else gate.stride(0), ptr(out), r.tokens, r.top,
-         width, ptr(h), dtype_code(h.dtype))
+         width, ptr(h), dtype_code(h.dtype), int(into is not None))
     return out
 
 

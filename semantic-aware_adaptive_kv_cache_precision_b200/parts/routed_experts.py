@@ -89,8 +89,9 @@ class RoutedExperts(Part):
                                               arena.view(p + "shared.up")])
             self.w_shared_down = arena.view(p + "shared.down")
 
-    def produce(self, h, step):
-        """The feed-forward's output, fp32 [T, hidden]."""
+    def produce(self, h, step, into=None):
+        """The feed-forward's output, fp32 [T, hidden]; with `into` (the fp32 stream) it is
+        added there by the kernel that sums a token's rows."""
         s = self.spec
         logits = mixture.router_logits(h, self.w_route)
         routing = mixture.route(logits, s.experts, s.top, s.identity, s.score == "softmax",
@@ -107,10 +108,10 @@ class RoutedExperts(Part):
             shared = ops.linear(mixture.clamped_act(both, s.shared.limit, s.shared.alpha),
                                 self.w_shared_down, out_dtype=torch.float32)
             gate = logits[:, self.outputs] if self.has_gate else None
-        return mixture.combine(products, routing, not s.weight_input, shared, gate, h)
+        return mixture.combine(products, routing, not s.weight_input, shared, gate, h, into)
 
     def forward(self, h, step, residual):
-        ops.add_into(residual, self.produce(h, step))
+        self.produce(h, step, into=residual)
 
 
 register_part("routed_experts", RoutedExperts)
