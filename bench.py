@@ -362,6 +362,24 @@ def kernel_case(name: str) -> int:
         step = SimpleNamespace(cu_seqlens=i32([0, n]), slots=i32([0]), sequences=1, max_new=n)
         run = lambda i: ops.selective_scan(x, dt, low, rank, rank + ns, ns, z, a_log, skip, state,
                                            step, run=64)
+    elif name == "retention_4096":
+        # retention over one prompt of 4,096 tokens at the `2k` size of `--design gesuvik` (16
+        # heads of 128 x 128, the whole head turned), walked in runs of 64 tokens: about 200 MB
+        from types import SimpleNamespace
+        import numpy as np
+        n, heads, dim, vdim = 4096, 16, 128, 128
+        proj = torch.randn(n, heads * (2 * dim + vdim), device=dev)
+        angle = np.arange(n)[:, None] * np.power(1e6, -2.0 * np.arange(dim // 2) / dim)[None, :]
+        cos = torch.tensor(np.cos(angle), dtype=torch.float32, device=dev)
+        sin = torch.tensor(np.sin(angle), dtype=torch.float32, device=dev)
+        less_one = -torch.rand(heads, device=dev) * 0.01
+        state = torch.zeros(1, heads, vdim, dim, device=dev)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        step = SimpleNamespace(cu_seqlens=i32([0, n]), slots=i32([0]), sequences=1, max_new=n,
+                               positions=torch.arange(n, dtype=torch.int32, device=dev))
+        run = lambda i: ops.decay_attention(proj, 0, heads * dim, 2 * heads * dim, heads, dim, vdim,
+                                            less_one, state, step, run=64, activation=False,
+                                            cos=cos, sin=sin, key_scale=dim ** -0.5)
     else:
         raise SystemExit(f"unknown kernel case {name}")
     for i in range(4):
@@ -953,8 +971,8 @@ def main() -> int:
     ap.add_argument("--design-sizes", default="1k,2k", help="which of: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--kernel", default=None,
                     help="run one kernel case for a profiler: gemm_gateup_b8, gemm_down_b8, "
-                         "gemm_head_b8, gemm_gated_2048, selective_scan_4096, attention_decode_b64, "
-                         "attention_prefill_2048")
+                         "gemm_head_b8, gemm_gated_2048, selective_scan_4096, retention_4096, "
+                         "attention_decode_b64, attention_prefill_2048")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
