@@ -321,18 +321,29 @@ struct FadeInput {
   float k_scale;
 };
 
-__device__ __forceinline__ float fade_input(const float* __restrict__ head, int i, int pos,
-                                            const FadeInput& in) {
-  float x = in.act ? silu(head[i]) : head[i];
-  if (i < in.rot) {
-    const int half = in.rot >> 1;
-    const bool low = i < half;
-    const int pair = low ? i : i - half;
-    const float other = in.act ? silu(head[low ? i + half : pair]) : head[low ? i + half : pair];
-    const float c = in.cos_t[(long long)pos * half + pair], sn = in.sin_t[(long long)pos * half + pair];
-    x = low ? x * c - other * sn : x * c + other * sn;
+__device__ __forceinline__ float fade_act(float x, int act) { return act ? silu(x) : x; }
+
+// One token's head of q or k from `head` (global) to `to` (shared), `padded` floats of which
+// the first `dim` are real, times `scale`; element `i` is this thread's. A rotated pair is
+// made by the thread of its lower half, which reads both numbers and the angle once.
+__device__ __forceinline__ void fade_stage(const float* __restrict__ head, float* __restrict__ to,
+                                           int i, int dim, int pos, float scale,
+                                           const FadeInput& in) {
+  const int half = in.rot >> 1;
+  if (i >= half && i < in.rot) return;                 // its partner's thread writes it
+  if (i >= dim) {
+    to[i] = 0.f;
+    return;
   }
-  return x;
+  const float x = fade_act(head[i], in.act);
+  if (i >= in.rot) {
+    to[i] = x * scale;
+    return;
+  }
+  const float y = fade_act(head[i + half], in.act);
+  const float c = in.cos_t[(long long)pos * half + i], sn = in.sin_t[(long long)pos * half + i];
+  to[i] = (x * c - y * sn) * scale;
+  to[i + half] = (y * c + x * sn) * scale;
 }
 
 // PHASE as in the selective scan: 0 walks a sequence's whole part of the step from the state in
@@ -351,6 +362,7 @@ __global__ void decay_attention_kernel(const float* __restrict__ proj, long long
                                        float* __restrict__ scratch, const FadeInput in) {
   extern __shared__ __align__(16) float shared[];
   const int padded = rs * RP;                       // dim rounded up to whole lanes
+  const int padded_shift = 31 - __clz(padded);
   float* qs = shared;                               // [kRun, padded]
   float* ks = qs + kRun * padded;                   // [kRun, padded]
   float* vs = ks + kRun * padded;                   // [kRun, cols]
@@ -378,11 +390,11 @@ __global__ void decay_attention_kernel(const float* __restrict__ proj, long long
     const int run = last - t0 < kRun ? last - t0 : kRun;
     __syncthreads();
     for (int e = threadIdx.x; e < run * padded; e += blockDim.x) {
-      const int tt = e / padded, i = e - tt * padded;
+      const int tt = e >> padded_shift, i = e & (padded - 1);     // (padded is a power of two)
       const float* row = proj + (long long)(t0 + tt) * stride + (long long)h * dim;
       const int pos = in.rot ? in.positions[t0 + tt] : 0;
-      if (PHASE != 1) qs[e] = i < dim ? fade_input(row + q_off, i, pos, in) : 0.f;
-      ks[e] = i < dim ? fade_input(row + k_off, i, pos, in) * in.k_scale : 0.f;
+      if (PHASE != 1) fade_stage(row + q_off, qs + tt * padded, i, dim, pos, 1.f, in);
+      fade_stage(row + k_off, ks + tt * padded, i, dim, pos, in.k_scale, in);
     }
     for (int e = threadIdx.x; e < run * cols; e += blockDim.x) {
       const int tt = e / cols, i = e - tt * cols;
@@ -397,10 +409,24 @@ __global__ void decay_attention_kernel(const float* __restrict__ proj, long long
     for (int tt = 0; tt < run; ++tt) {
       const float v = vs[tt * cols + j];
       float o = 0.f;
+      // a lane's rows of k and q lie together: four at a time (RP is 4 or 8; the offsets are
+      // multiples of four floats); S + (decay - 1) S in one rounding, then k v added by the next
+      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * padded + r * RP);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * padded + r * RP);
 #pragma unroll
-      for (int k = 0; k < RP; ++k) {
-        s[k] += fmaf(fade, s[k], ks[tt * padded + r * RP + k] * v);
-        if (PHASE != 1) o = fmaf(s[k], qs[tt * padded + r * RP + k], o);
+      for (int k = 0; k < RP; k += 4) {
+        const float4 kk = k4[k >> 2];
+        s[k] = fmaf(kk.x, v, fmaf(fade, s[k], s[k]));
+        s[k + 1] = fmaf(kk.y, v, fmaf(fade, s[k + 1], s[k + 1]));
+        s[k + 2] = fmaf(kk.z, v, fmaf(fade, s[k + 2], s[k + 2]));
+        s[k + 3] = fmaf(kk.w, v, fmaf(fade, s[k + 3], s[k + 3]));
+        if (PHASE != 1) {
+          const float4 qq = q4[k >> 2];
+          o = fmaf(s[k], qq.x, o);
+          o = fmaf(s[k + 1], qq.y, o);
+          o = fmaf(s[k + 2], qq.z, o);
+          o = fmaf(s[k + 3], qq.w, o);
+        }
       }
       if (PHASE != 1) {
         for (int d = rs >> 1; d > 0; d >>= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
