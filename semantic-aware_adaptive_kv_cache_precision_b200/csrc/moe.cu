@@ -7,7 +7,8 @@
 //            experts that have weights are identity experts: they take no rows, and combine
 //            adds the token's own input times the weight for them
 //   plan     one block: where each expert's rows begin and which (expert, first row) every
-//            tile of `TM` rows of the grouped products covers
+//            tile of `TM` rows of the grouped products covers (for a step of few tokens the
+//            same block chooses for all of them first: one launch instead of two)
 //   gather   the experts' input rows, sorted by expert: x * weight (the weight multiplies an
 //            expert's INPUT) rounded once to the activations' type
 //   products out = rows x W[e]^T for every tile, with the weights of the tile's expert:
@@ -51,14 +52,12 @@ __global__ void logits_kernel(const T* __restrict__ h, const float* __restrict__
 // `experts`: the router's outputs; the first `real` of them have weights. softmax 0: the score
 // is sigmoid(z); 1: exp(z - max) / sum over all outputs. bias (null: none): added to the score
 // for the choice. Without a bias the sigmoid's order is the logits' own, and they are compared.
-__global__ void route_kernel(const float* __restrict__ logits, long long ld, int experts, int top,
-                             int32_t* __restrict__ chosen, float* __restrict__ weights,
-                             int32_t* __restrict__ counts, int32_t* __restrict__ rank,
-                             int tokens, int real, int softmax, const float* __restrict__ bias) {
-  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (t >= tokens) return;
-  const float* z = logits + t * ld;
+__device__ __forceinline__ void route_token(const float* __restrict__ z, int experts, int top,
+                                            int32_t* __restrict__ chosen,
+                                            float* __restrict__ weights,
+                                            int32_t* counts, int32_t* __restrict__ rank,
+                                            int real, int softmax,
+                                            const float* __restrict__ bias, int lane) {
   float top_z = -INFINITY, total = 1.f;
   if (softmax) {
     for (int e = lane; e < experts; e += 32) top_z = fmaxf(top_z, z[e]);
@@ -95,17 +94,30 @@ __global__ void route_kernel(const float* __restrict__ logits, long long ld, int
     if (at == 0x7fffffff) at = k;                  // (a row without a finite logit)
     if ((at & 31) == lane) taken |= 1u << (at >> 5);
     if (lane == 0) {
-      chosen[t * top + k] = at;
-      weights[t * top + k] = score(z[at]);
-      rank[t * top + k] = at < real ? atomicAdd(counts + at, 1) : -1;
+      chosen[k] = at;
+      weights[k] = score(z[at]);
+      rank[k] = at < real ? atomicAdd(counts + at, 1) : -1;
     }
   }
 }
 
-__global__ void plan_kernel(int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
-                            int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row,
-                            int32_t* __restrict__ n_tiles, int experts, int max_tiles) {
-  extern __shared__ int32_t base[];                // [experts + 1] first tile of each expert
+__global__ void route_kernel(const float* __restrict__ logits, long long ld, int experts, int top,
+                             int32_t* __restrict__ chosen, float* __restrict__ weights,
+                             int32_t* __restrict__ counts, int32_t* __restrict__ rank,
+                             int tokens, int real, int softmax, const float* __restrict__ bias) {
+  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  if (t >= tokens) return;
+  route_token(logits + t * ld, experts, top, chosen + t * top, weights + t * top, counts,
+              rank + t * top, real, softmax, bias, threadIdx.x & 31);
+}
+
+// Where each expert's rows begin and the tiles of the grouped products, from the experts'
+// row counts; `base`: [experts + 1] ints of shared memory. The whole block calls it.
+__device__ __forceinline__ void plan_tiles(const int32_t* counts, int32_t* __restrict__ offsets,
+                                           int32_t* __restrict__ tile_expert,
+                                           int32_t* __restrict__ tile_row,
+                                           int32_t* __restrict__ n_tiles, int experts,
+                                           int max_tiles, int32_t* base) {
   if (threadIdx.x == 0) {
     int rows = 0, tiles = 0;
     for (int e = 0; e < experts; ++e) {
@@ -127,6 +139,34 @@ __global__ void plan_kernel(int32_t* __restrict__ counts, int32_t* __restrict__ 
       tile_row[base[e] + i] = offsets[e] + i * TM;
     }
   }
+}
+
+// A step of few tokens: one block chooses for every token (a warp a token in turn, counting
+// rows in shared memory) and then plans, in one launch.
+__global__ void __launch_bounds__(256)
+route_plan_kernel(const float* __restrict__ logits, long long ld, int experts, int top,
+                  int32_t* __restrict__ chosen, float* __restrict__ weights,
+                  int32_t* __restrict__ rank, int tokens, int real, int softmax,
+                  const float* __restrict__ bias, int32_t* __restrict__ offsets,
+                  int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row,
+                  int32_t* __restrict__ n_tiles, int max_tiles) {
+  extern __shared__ int32_t shared_ints[];         // counts [real], then base [real + 1]
+  int32_t* counts = shared_ints;
+  for (int e = threadIdx.x; e < real; e += blockDim.x) counts[e] = 0;
+  __syncthreads();
+  for (int t = threadIdx.x >> 5; t < tokens; t += blockDim.x >> 5)
+    route_token(logits + t * ld, experts, top, chosen + (long long)t * top,
+                weights + (long long)t * top, counts, rank + (long long)t * top, real, softmax,
+                bias, threadIdx.x & 31);
+  __syncthreads();
+  plan_tiles(counts, offsets, tile_expert, tile_row, n_tiles, real, max_tiles, counts + real);
+}
+
+__global__ void plan_kernel(int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                            int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row,
+                            int32_t* __restrict__ n_tiles, int experts, int max_tiles) {
+  extern __shared__ int32_t base[];                // [experts + 1] first tile of each expert
+  plan_tiles(counts, offsets, tile_expert, tile_row, n_tiles, experts, max_tiles, base);
   __syncthreads();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;     // for the next step
 }
@@ -391,6 +431,21 @@ SAKV_EXPORT int sakv_moe_route(const float* logits, long long ld, int experts, i
   const long long blocks = ((long long)tokens * 32 + threads - 1) / threads;
   return launch_ordered(route_kernel, dim3((unsigned)blocks), dim3(threads), 0, stream, logits, ld,
                         experts, top, chosen, weights, counts, rank, tokens, real, softmax, bias);
+}
+
+// `sakv_moe_route` and `sakv_moe_plan` in one launch of one block, for steps of few tokens
+// (the rows' counts live in shared memory: no `counts` argument).
+SAKV_EXPORT int sakv_moe_route_plan(const float* logits, long long ld, int experts, int top,
+                                    int32_t* chosen, float* weights, int32_t* rank, int tokens,
+                                    int real, int softmax, const float* bias, int32_t* offsets,
+                                    int32_t* tile_expert, int32_t* tile_row, int32_t* n_tiles,
+                                    int max_tiles, cudaStream_t stream) {
+  if (tokens <= 0 || experts <= 0 || experts > 1024 || top <= 0 || top > experts || top > 32 ||
+      ld < experts || real <= 0 || real > experts || max_tiles <= 0)
+    return cudaErrorInvalidValue;
+  return launch_ordered(route_plan_kernel, dim3(1), dim3(256), (size_t)(2 * real + 1) * 4, stream,
+                        logits, ld, experts, top, chosen, weights, rank, tokens, real, softmax,
+                        bias, offsets, tile_expert, tile_row, n_tiles, max_tiles);
 }
 
 // out[t, o] = sum_i h[t, i] w[o, i] in fp32: h [tokens, width] of `dtype`, w fp32 [outputs,

@@ -57,6 +57,7 @@ SIGNATURES = {
     "sakv_moe_logits": ("moe", [P, I, P, P, I, I, I, P]),
     "sakv_moe_route": ("moe", [P, L, I, I, P, P, P, P, I, I, I, P, P]),
     "sakv_moe_plan": ("moe", [P, P, P, P, P, I, I, P]),
+    "sakv_moe_route_plan": ("moe", [P, L, I, I, P, P, P, I, I, I, P, P, P, P, P, I, P]),
     "sakv_moe_gather": ("moe", [P, I, P, P, P, P, P, P, I, I, I, I, P]),
     "sakv_moe_product": ("moe", [P, I, P, P, L, P, P, P, P, I, P, I, I, I, F, F, P]),
     "sakv_clamped_act": ("moe", [P, P, I, I, I, F, F, P]),

@@ -24,6 +24,9 @@ class Routing:
 
 _counts: dict = {}
 
+#: up to this many tokens one block chooses for all of them and plans, in one launch
+ROUTE_IN_ONE_BLOCK = 64
+
 
 def tile_rows() -> int:
     return plain_function("sakv_moe_tile_rows")()
@@ -70,6 +73,11 @@ def route(logits: torch.Tensor, experts: int, top: int, identity: int = 0,
     r.offsets, r.n_tiles = plan[:experts + 1], plan[experts + 1:experts + 2]
     r.tile_expert = plan[experts + 2:experts + 2 + r.max_tiles]
     r.tile_row = plan[experts + 2 + r.max_tiles:]
+    if 0 < tokens <= ROUTE_IN_ONE_BLOCK:
+        call("sakv_moe_route_plan", ptr(logits), logits.stride(0), outputs, top, ptr(r.chosen),
+             ptr(r.weights), ptr(r.rank), tokens, experts, int(bool(softmax)), ptr(bias),
+             ptr(r.offsets), ptr(r.tile_expert), ptr(r.tile_row), ptr(r.n_tiles), r.max_tiles)
+        return r
     call("sakv_moe_route", ptr(logits), logits.stride(0), outputs, top, ptr(r.chosen),
          ptr(r.weights), ptr(counts), ptr(r.rank), tokens, experts, int(bool(softmax)), ptr(bias))
     call("sakv_moe_plan", ptr(counts), ptr(r.offsets), ptr(r.tile_expert), ptr(r.tile_row),

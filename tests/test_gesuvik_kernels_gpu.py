@@ -192,7 +192,7 @@ def plain_latent_attention(qa, qb, rows, rank, scale, window, sinks, gate):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,rank,rot,window", [(4, 40, 8, 37), (5, 36, 6, 100), (2, 512, 64, 128),
-                                                   (1, 16, 32, None), (3, 24, 8, 64), (8, 96, 32, 72),
+                                                   (1, 16, 32, None), (3, 24, 8, 64), (6, 80, 16, 70),
                                                    (2, 8, 2, 1)])
 def test_keys_at_the_window_s_edge_over_a_cached_latent(dtype, heads, rank, rot, window):
     """Three keys stand out: for one asker the oldest key of its window and the one before it,

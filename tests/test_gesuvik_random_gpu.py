@@ -33,7 +33,7 @@ def draw(seed, all_chosen=False):
                    shared)
 
     def window():
-        return pick([None, 1, 2, 7, 31, 64, 65, 72, 96, 130, 500])
+        return pick([None, 1, 2, 7, 31, 64, 65, 70, 96, 130, 500])
 
     layers = []
     for _ in range(int(rng.integers(1, 7))):
